@@ -54,9 +54,11 @@ def known_architectures() -> List[str]:
 
 def config_from_dict(d: Mapping[str, Any]) -> ModelConfig:
     archs = d.get("architectures")
+    if not archs and isinstance(d.get("architecture"), str):
+        archs = [d["architecture"]]           # some families name theirs under a key in the singular
     if not archs or not isinstance(archs, (list, tuple)):
         raise ConfigError(
-            "config.json has no 'architectures' list; known architectures: "
+            "config.json has no 'architectures' list (nor an 'architecture' name); known architectures: "
             + ", ".join(known_architectures())
         )
     name = archs[0]

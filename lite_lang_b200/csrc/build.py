@@ -34,7 +34,8 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-r
 
 # name -> (sources, definitions)
 LIBRARIES: Dict[str, Tuple[Tuple[str, ...], Tuple[str, ...]]] = {
-    "core": (("embedding.cu", "norm.cu", "rope.cu", "activation.cu", "sampling.cu", "attention_generic.cu"), ()),
+    "core": (("embedding.cu", "norm.cu", "layernorm.cu", "rope.cu", "activation.cu", "sampling.cu",
+              "attention_generic.cu"), ()),
     "attn_mma": (("attention_mma.cu", "attention_prefill.cu", "attention_decode.cu"), ()),
     "gemm_smallm": (("gemm_smallm.cu",), ()),
     "gemm_stream": (("gemm_stream.cu",), ()),
@@ -42,6 +43,9 @@ LIBRARIES: Dict[str, Tuple[Tuple[str, ...], Tuple[str, ...]]] = {
     "gemm_pair": (("gemm_pair.cu",), ()),
     "attn_tc": (("attention_prefill_tc.cu",), ()),
     "attn_mma_static": (("attention_mma_static.cu",), ()),
+    "delta_rule": (("delta_rule.cu",), ()),
+    "latent_attn": (("latent_attention.cu",), ()),
+    "moe": (("moe.cu",), ()),
 }
 
 _INCLUDE = re.compile(r'^\s*#\s*include\s+"([^"]+)"', re.M)

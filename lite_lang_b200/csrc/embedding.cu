@@ -35,6 +35,29 @@ extern "C" int ll_embed_gather(int dtype, void* out, const void* table, const in
   return LL_LAUNCH_RESULT();
 }
 
+// Token embedding into a float32 residual stream, times a constant: out[t, :] = scale * table[ids[t], :].
+template <typename T>
+__global__ void embed_scaled_f32_kernel(float* __restrict__ out, const T* __restrict__ table,
+                                        const int* __restrict__ ids, int hidden, int vocab, float scale, int* status) {
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool ok = (id >= 0 && id < vocab);
+  if (!ok && threadIdx.x == 0) set_status(status, LL_ERR_TOKEN_RANGE);
+  float* dst = out + (size_t)t * hidden;
+  const T* src = table + (size_t)(ok ? id : 0) * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? to_f32<T>(src[i]) * scale : 0.f;
+}
+
+extern "C" int ll_embed_scaled_f32(int dtype, float* out, const void* table, const int* ids, int num_tokens,
+                                   int hidden, int vocab, float scale, int* status, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  LL_DISPATCH_DTYPE(dtype, ll_launch(embed_scaled_f32_kernel<T>, dim3(num_tokens), dim3(128), 0, stream, out,
+                                     (const T*)table, ids, hidden, vocab, scale, status));
+  return LL_LAUNCH_RESULT();
+}
+
 // Token ids that are still on the device: ids[i] = results[feed[i]] where feed[i] >= 0.  A decode step that
 // is launched before the host has seen the tokens sampled by the step before takes them from that step's
 // result buffer this way.  A feed index outside [0, max_results) leaves ids[i] as the host wrote it.

@@ -1,0 +1,64 @@
+// Layer norm with a weight and no bias over a float32 residual stream, fused with the residual sum.
+//
+//   r = residual + (d1 + d2)                  (float32; d1, d2 optional, stored as T)
+//   y = (r - mean(r)) / sqrt(var(r) + eps) * w       (var = mean of the squared deviations)
+//
+// The residual stream stays float32 whatever the storage type T of the activations is: r is
+// written back unrounded, and y is rounded once to T.  With `rows` given only those rows are
+// read and nothing is written back (the last norm before the logits).  One block per row; the
+// row is kept in shared memory between the passes (mean, then deviations: two passes, so that
+// the variance is not a difference of large numbers).
+#include "common.cuh"
+
+template <typename T>
+__global__ void add_layernorm_kernel(T* __restrict__ out, float* __restrict__ residual, const T* __restrict__ d1,
+                                     const T* __restrict__ d2, const float* __restrict__ w, float eps, int hidden,
+                                     const int* __restrict__ rows, int write_residual) {
+  extern __shared__ float row[];
+  __shared__ float scratch[32];
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const int i_out = blockIdx.x;
+  const int r = rows ? rows[i_out] : i_out;
+  float* res = residual + (size_t)r * hidden;
+  const T* a = d1 ? d1 + (size_t)r * hidden : nullptr;
+  const T* b = d2 ? d2 + (size_t)r * hidden : nullptr;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = res[i];
+    if (a || b) {
+      float d = a ? to_f32<T>(a[i]) : 0.f;
+      if (b) d += to_f32<T>(b[i]);
+      v += d;
+      if (write_residual) res[i] = v;
+    }
+    row[i] = v;
+    s += v;
+  }
+  const float mean = block_sum(s, scratch) / (float)hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float c = row[i] - mean;
+    ss += c * c;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)hidden + eps);
+  T* o = out + (size_t)i_out * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<T>((row[i] - mean) * inv * w[i]);
+}
+
+// out: [n_out, hidden] of T; residual: float32 [tokens, hidden]; d1, d2: T [tokens, hidden] or null.
+extern "C" int ll_add_layernorm(int dtype, void* out, float* residual, const void* d1, const void* d2, const float* w,
+                                float eps, int n_out, int hidden, const int* rows, int write_residual,
+                                cudaStream_t stream) {
+  if (n_out <= 0) return 0;
+  if (hidden <= 0) return (int)cudaErrorInvalidValue;
+  const size_t smem = sizeof(float) * (size_t)hidden;
+  const int threads = hidden >= 2048 ? 512 : hidden >= 512 ? 256 : 128;
+  LL_DISPATCH_DTYPE(dtype, {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(add_layernorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ll_launch(add_layernorm_kernel<T>, dim3(n_out), dim3(threads), smem, stream, (T*)out, residual, (const T*)d1,
+              (const T*)d2, w, eps, hidden, rows, write_residual);
+  });
+  return LL_LAUNCH_RESULT();
+}

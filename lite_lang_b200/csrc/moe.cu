@@ -1,0 +1,141 @@
+// Routed feed-forward (mixture of experts): the router and the activation between the two products.
+//
+// Router, per token, all in float32: logits z = Wr x over the experts, scores by softmax (or sigmoid) over
+// all experts, the `top` experts with the largest scores (ties: the lower index), their weights the scores
+// themselves or the scores divided by their sum.  The result is a dense row of weights per token, zero for
+// experts that were not chosen, plus the chosen indices and weights.
+//
+// The experts' first products run as one product over all experts' rows (an always-on expert's rows first);
+// `moe_act` then applies the activation and multiplies every hidden unit by the weight of its expert for that
+// token (1 for the always-on rows, 0 for experts not chosen), so that one second product over all hidden units
+// gives the weighted sum of the chosen experts' outputs plus the always-on expert's.
+#include "common.cuh"
+
+#define MOE_MAX_E 256
+
+// Wr: float32 [E, hidden]; x: T [tokens, hidden]; gates: float32 [tokens, E]; top_idx int32 / top_w float32
+// [tokens, top].  score_fn: 0 softmax, 1 sigmoid.  One warp per token.
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_router_kernel(const T* __restrict__ x, long x_stride, const float* __restrict__ Wr, float* __restrict__ gates,
+                  int* __restrict__ top_idx, float* __restrict__ top_w, int num_tokens, int hidden, int E, int top,
+                  int score_fn, int renormalize) {
+  __shared__ float z_s[4][MOE_MAX_E];
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= num_tokens) return;
+  float* z = z_s[warp];
+  const T* xr = x + (size_t)t * x_stride;
+  for (int e = 0; e < E; ++e) {
+    const float* wr = Wr + (size_t)e * hidden;
+    float acc = 0.f;
+    for (int i = lane; i < hidden; i += 32) acc = fmaf(wr[i], to_f32<T>(xr[i]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) z[e] = acc;
+  }
+  __syncwarp();
+  if (score_fn == 0) {
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += expf(z[e] - m);
+    sum = warp_sum(sum);
+    for (int e = lane; e < E; e += 32) z[e] = expf(z[e] - m) / sum;
+  } else {
+    for (int e = lane; e < E; e += 32) z[e] = 1.0f / (1.0f + expf(-z[e]));
+  }
+  __syncwarp();
+  float* gr = gates + (size_t)t * E;
+  for (int e = lane; e < E; e += 32) gr[e] = 0.f;
+  __syncwarp();
+  float total = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int arg = E;
+    for (int e = lane; e < E; e += 32) {
+      const float v = z[e];
+      if (v > best) {   // (a lane walks upwards, so it keeps its lowest index among equals)
+        best = v;
+        arg = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) {
+        best = ob;
+        arg = oa;
+      }
+    }
+    if (arg >= E) break;
+    if (lane == 0) {
+      top_idx[(size_t)t * top + k] = arg;
+      top_w[(size_t)t * top + k] = best;
+      gr[arg] = best;
+      z[arg] = -INFINITY;
+    }
+    total += best;
+    __syncwarp();
+  }
+  if (renormalize && total > 0.f) {
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) gr[e] = gr[e] / total;
+    for (int k = lane; k < top; k += 32) top_w[(size_t)t * top + k] /= total;
+  }
+}
+
+// act: 0 relu(z)^2, 1 silu(z), 2 gelu_tanh(z).
+__device__ __forceinline__ float moe_activation(float z, int act) {
+  if (act == 0) {
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+  }
+  if (act == 1) return z / (1.0f + expf(-z));
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// h: T [tokens, shared_ff + E * ff] in place: h = act(h) * weight, weight 1 for the first shared_ff columns,
+// gates[t, (col - shared_ff) / ff] for the rest.
+template <typename T>
+__global__ void moe_act_kernel(T* __restrict__ h, const float* __restrict__ gates, long total, int width, int shared_ff,
+                               int ff, int E, int act) {
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const long step = (long)gridDim.x * blockDim.x;
+  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += step) {
+    const long t = idx / width;
+    const int c = (int)(idx - t * width);
+    const float w = c < shared_ff ? 1.f : gates[t * E + (c - shared_ff) / ff];
+    // an expert that was not chosen contributes an exact zero whatever its first product gave
+    h[idx] = from_f32<T>(w == 0.f ? 0.f : moe_activation(to_f32<T>(h[idx]), act) * w);
+  }
+}
+
+extern "C" int ll_moe_router(int dtype, const void* x, long x_stride, const float* Wr, float* gates, int* top_idx,
+                             float* top_w, int num_tokens, int hidden, int E, int top, int score_fn, int renormalize,
+                             cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (E <= 0 || E > MOE_MAX_E || top <= 0 || top > E || hidden <= 0) return (int)cudaErrorInvalidValue;
+  LL_DISPATCH_DTYPE(dtype, ll_launch(moe_router_kernel<T>, dim3((num_tokens + 3) / 4), dim3(128), 0, stream,
+                                     (const T*)x, x_stride, Wr, gates, top_idx, top_w, num_tokens, hidden, E, top,
+                                     score_fn, renormalize));
+  return LL_LAUNCH_RESULT();
+}
+
+extern "C" int ll_moe_act(int dtype, void* h, const float* gates, int num_tokens, int shared_ff, int ff, int E, int act,
+                          int sms, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const int width = shared_ff + E * ff;
+  if (width <= 0 || (E > 0 && ff <= 0)) return (int)cudaErrorInvalidValue;
+  const long total = (long)num_tokens * width;
+  const long most = (long)(sms > 0 ? sms : 148) * 16;
+  const long want = (total + 255) / 256;
+  const int blocks = (int)(want < most ? want : most);
+  LL_DISPATCH_DTYPE(dtype, ll_launch(moe_act_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)h, gates, total, width,
+                                     shared_ff, ff, E, act));
+  return LL_LAUNCH_RESULT();
+}

@@ -1,5 +1,6 @@
 """Architectures.  Importing this package registers each of them."""
-from . import qwen2  # noqa: F401
+from . import nevurax, qwen2  # noqa: F401
+from .nevurax import NevuraxConfig
 from .qwen2 import Qwen2Config
 
-__all__ = ["Qwen2Config"]
+__all__ = ["NevuraxConfig", "Qwen2Config"]

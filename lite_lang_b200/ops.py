@@ -964,3 +964,181 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
     if out is not None:
         return torch.mm(x, weight.t(), out=out)
     return torch.mm(x, weight.t())
+
+
+# --------------------------------------------------------------------------
+# float32 residual stream: scaled embedding and layer norm
+# --------------------------------------------------------------------------
+def embed_scaled_f32(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, scale: float,
+                     status: Optional[torch.Tensor]) -> None:
+    """out[t] = scale * table[ids[t]] as float32 rows (the residual stream of a model that keeps it in 32-bit)."""
+    _need_cuda(out, table, ids)
+    _i32(ids, "ids")
+    _f32(out, "out")
+    _need(table.is_contiguous() and out.shape[1] == table.shape[1] and out.shape[0] >= ids.numel(),
+          "embed_scaled_f32: shapes")
+    core().call("ll_embed_scaled_f32", c_int(_dtype_code(table)), _ptr(out), _ptr(table), _ptr(ids),
+                c_int(ids.numel()), c_int(table.shape[1]), c_int(table.shape[0]), c_float(scale), _ptr(status),
+                _stream())
+
+
+def add_layernorm(out: torch.Tensor, residual: torch.Tensor, d1: Optional[torch.Tensor], d2: Optional[torch.Tensor],
+                  weight: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """residual (float32) += d1 + d2 (written back unless ``rows`` selects rows); out = layer norm of it
+    times ``weight``, in ``out``'s dtype."""
+    _need_cuda(out, residual, d1, d2, weight, rows)
+    _f32(weight, "norm weight")
+    _f32(residual, "residual")
+    _i32(rows, "rows")
+    hidden = residual.shape[1]
+    for d in (d1, d2):
+        if d is not None:
+            _need(d.dtype == out.dtype and d.is_contiguous() and tuple(d.shape) == tuple(residual.shape),
+                  "add_layernorm: a delta is [tokens, hidden] of the output's dtype")
+    n_out = rows.numel() if rows is not None else residual.shape[0]
+    _need(out.is_contiguous() and out.shape[0] >= n_out and out.shape[1] == hidden and weight.numel() == hidden,
+          "add_layernorm: out shape")
+    core().call("ll_add_layernorm", c_int(_dtype_code(out)), _ptr(out), _ptr(residual), _ptr(d1), _ptr(d2),
+                _ptr(weight), c_float(eps), c_int(n_out), c_int(hidden), _ptr(rows), c_int(1 if rows is None else 0),
+                _stream())
+
+
+# --------------------------------------------------------------------------
+# gated delta rule
+# --------------------------------------------------------------------------
+def delta_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, b_off: int, a_in: torch.Tensor,
+                  conv_q: torch.Tensor, conv_k: torch.Tensor, conv_v: torch.Tensor, A_log: torch.Tensor,
+                  dt_bias: torch.Tensor, state: torch.Tensor, tail_off: int, step, qn: torch.Tensor, kn: torch.Tensor,
+                  vc: torch.Tensor, beta: torch.Tensor, g: torch.Tensor, H: int, Hk: int, dk: int, dv: int, taps: int,
+                  per_channel: bool) -> None:
+    """Convolution + SiLU of q, k, v (continuing from the records' last inputs), unit vectors, beta and decay of
+    the step's tokens into float32 buffers; then the records' last ``taps - 1`` inputs are brought up to date."""
+    _need_cuda(proj, a_in, conv_q, conv_k, conv_v, A_log, dt_bias, state, qn, kn, vc, beta, g)
+    for t, nm in ((conv_q, "conv_q"), (conv_k, "conv_k"), (conv_v, "conv_v"), (A_log, "A_log"), (dt_bias, "dt_bias"),
+                  (state, "state"), (qn, "qn"), (kn, "kn"), (vc, "vc"), (beta, "beta"), (g, "g")):
+        _f32(t, nm)
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and a_in.stride(1) == 1 and a_in.dtype == proj.dtype,
+          "delta_prepare: projections are rows of one dtype")
+    _need(state.dim() == 2 and state.shape[1] == tail_off + (taps - 1) * (2 * Hk * dk + H * dv),
+          "delta_prepare: the state record is S followed by the convolutions' last inputs")
+    n = proj.shape[0]
+    load_library("delta_rule").call(
+        "ll_delta_prepare", c_int(_dtype_code(proj)), _ptr(proj), c_long(proj.stride(0)), c_int(q_off), c_int(k_off),
+        c_int(v_off), c_int(b_off), _ptr(a_in), c_long(a_in.stride(0)), _ptr(conv_q), _ptr(conv_k), _ptr(conv_v),
+        _ptr(A_log), _ptr(dt_bias), _ptr(state), c_long(state.stride(0)), c_long(tail_off), _ptr(step.token_req),
+        _ptr(step.cu_q), _ptr(step.ctx_len), _ptr(step.req_slot), _ptr(step.positions), _ptr(qn), _ptr(kn), _ptr(vc),
+        _ptr(beta), _ptr(g), c_int(n), c_int(step.num_entries), c_int(H), c_int(Hk), c_int(dk), c_int(dv),
+        c_int(taps), c_int(1 if per_channel else 0), _stream())
+
+
+def delta_recurrence(qn: torch.Tensor, kn: torch.Tensor, vc: torch.Tensor, beta: torch.Tensor, g: torch.Tensor,
+                     state: torch.Tensor, step, o: torch.Tensor, H: int, Hk: int, dk: int, dv: int,
+                     per_channel: bool) -> None:
+    """The scan of every entry's tokens through its request's state; o float32 [tokens, H, dv]."""
+    _need_cuda(qn, kn, vc, beta, g, state, o)
+    _need(dk <= 256, f"delta rule: key heads of {dk} channels are wider than the scan kernel takes (256)")
+    load_library("delta_rule").call(
+        "ll_delta_recurrence", _ptr(qn), _ptr(kn), _ptr(vc), _ptr(beta), _ptr(g), _ptr(state), c_long(state.stride(0)),
+        _ptr(step.cu_q), _ptr(step.req_slot), _ptr(o), c_int(step.num_entries), c_int(H), c_int(Hk), c_int(dk),
+        c_int(dv), c_int(1 if per_channel else 0), _stream())
+
+
+def delta_out(out: torch.Tensor, o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, eps: float, H: int,
+              dv: int, gate_act: int) -> None:
+    """out = o / rms(o over dv) * weight * act(gate); act 0 SiLU, 1 sigmoid."""
+    _need_cuda(out, o, weight, gate)
+    _f32(o, "o")
+    _f32(weight, "weight")
+    _need(out.is_contiguous() and gate.stride(1) == 1 and gate.dtype == out.dtype, "delta_out: layout")
+    load_library("delta_rule").call(
+        "ll_delta_out", c_int(_dtype_code(out)), _ptr(out), _ptr(o), _ptr(weight), _ptr(gate), c_long(gate.stride(0)),
+        c_float(eps), c_int(out.shape[0]), c_int(H), c_int(dv), c_int(gate_act), _stream())
+
+
+# --------------------------------------------------------------------------
+# latent attention
+# --------------------------------------------------------------------------
+def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, norm_w: torch.Tensor, eps: float, freq: torch.Tensor,
+                   rot_dims: int, positions: torch.Tensor, slot_map: Optional[torch.Tensor], cache: torch.Tensor,
+                   q_rot: torch.Tensor, H: int, d: int, r: int, R: int, status: Optional[torch.Tensor]) -> None:
+    """Per token: the latent's RMS norm and the rotated key part into the cache row, and every head's rotated
+    query part into ``q_rot`` (float32 [tokens, H, r])."""
+    _need_cuda(proj, norm_w, freq, positions, slot_map, cache, q_rot)
+    _f32(norm_w, "norm_w")
+    _f32(freq, "freq")
+    _f32(q_rot, "q_rot")
+    _i32(positions, "positions")
+    _i32(slot_map, "slot_map")
+    _need(proj.stride(1) == 1 and cache.is_contiguous() and cache.dtype == proj.dtype and cache.shape[-1] == R + r
+          and cache.shape[1] == 1, "latent_prepare: the cache plane is [pages, 1, page, latent + rotated]")
+    load_library("latent_attn").call(
+        "ll_latent_prepare", c_int(_dtype_code(proj)), _ptr(proj), c_long(proj.stride(0)), c_int(q_off), c_int(kv_off),
+        _ptr(norm_w), c_float(eps), _ptr(freq), c_int(rot_dims), _ptr(positions), _ptr(slot_map), _ptr(cache),
+        c_long(cache.shape[0] * cache.shape[2]), _ptr(q_rot), c_int(proj.shape[0]), c_int(H), c_int(d), c_int(r),
+        c_int(R), _ptr(status), _stream())
+
+
+def latent_attention(out: torch.Tensor, qa: torch.Tensor, q_rot: torch.Tensor, cache: torch.Tensor,
+                     block_table: torch.Tensor, step, H: int, R: int, r: int, page_size: int,
+                     window: Optional[int], scale: float) -> None:
+    """Attention in the latent space.  ``qa`` float32 [H, tokens, R] (any strides with unit inner stride),
+    ``out`` [H, tokens, R] of the cache's dtype (likewise): sum_j p_j c_j per head."""
+    _need_cuda(out, qa, q_rot, cache, block_table)
+    _need(qa.dtype == torch.float32 and qa.stride(2) == 1 and out.stride(2) == 1 and out.dtype == cache.dtype,
+          "latent_attention: layouts")
+    _need(R <= 512, f"latent_attention: a latent of {R} numbers is wider than the kernel takes (512)")
+    n = qa.shape[1]
+    load_library("latent_attn").call(
+        "ll_latent_attention", c_int(_dtype_code(out)), _ptr(out), c_long(out.stride(0)), c_long(out.stride(1)),
+        _ptr(qa), c_long(qa.stride(0)), c_long(qa.stride(1)), _ptr(q_rot), _ptr(cache), _ptr(block_table),
+        c_int(block_table.stride(0)), _ptr(step.token_req), _ptr(step.req_slot), _ptr(step.positions), c_int(n),
+        c_int(H), c_int(R), c_int(r), c_int(page_size), c_int(cache.shape[0]), c_int(window or 0), c_float(scale),
+        _ptr(step.status), _stream())
+
+
+def batched_heads(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
+                  out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Library batched product over heads: a [H, n, k] times b [H, k, m] (any strides a BLAS takes); float32
+    operands give a true float32 product, bfloat16 operands accumulate in float32."""
+    if a.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
+        raise RuntimeError("TF32 is on; call ops.configure_matmul_precision() before a float32 product")
+    if out is not None:
+        return torch.bmm(a, b, out=out)
+    if out_dtype is not None and out_dtype != a.dtype:
+        return torch.bmm(a, b, out_dtype=out_dtype)
+    return torch.bmm(a, b)
+
+
+# --------------------------------------------------------------------------
+# routed feed-forward
+# --------------------------------------------------------------------------
+MOE_SCORE = {"softmax": 0, "sigmoid": 1}
+MOE_ACT = {"relu2": 0, "silu": 1, "gelu_tanh": 2}
+
+
+def moe_router(x: torch.Tensor, w_router: torch.Tensor, gates: torch.Tensor, top_idx: torch.Tensor,
+               top_w: torch.Tensor, top: int, score: str = "softmax", renormalize: bool = False) -> None:
+    """Scores over the experts in float32 and the ``top`` largest: ``gates`` float32 [tokens, E] (zero where an
+    expert was not chosen), ``top_idx`` int32 and ``top_w`` float32 [tokens, top]."""
+    _need_cuda(x, w_router, gates, top_idx, top_w)
+    _f32(w_router, "router weight")
+    _f32(gates, "gates")
+    _f32(top_w, "top_w")
+    _i32(top_idx, "top_idx")
+    E, hidden = w_router.shape
+    _need(E <= 256, f"moe_router: {E} experts are more than the kernel takes (256)")
+    _need(x.stride(1) == 1 and x.shape[1] == hidden, "moe_router: x rows")
+    load_library("moe").call(
+        "ll_moe_router", c_int(_dtype_code(x)), _ptr(x), c_long(x.stride(0)), _ptr(w_router), _ptr(gates),
+        _ptr(top_idx), _ptr(top_w), c_int(x.shape[0]), c_int(hidden), c_int(E), c_int(top), c_int(MOE_SCORE[score]),
+        c_int(1 if renormalize else 0), _stream())
+
+
+def moe_act(h: torch.Tensor, gates: torch.Tensor, shared_ff: int, ff: int, E: int, act: str) -> None:
+    """In place on the first product over all experts' rows: activation times the expert's weight for the token."""
+    _need_cuda(h, gates)
+    _f32(gates, "gates")
+    _need(h.is_contiguous() and h.shape[1] == shared_ff + E * ff, "moe_act: h is [tokens, shared + experts * ff]")
+    load_library("moe").call("ll_moe_act", c_int(_dtype_code(h)), _ptr(h), _ptr(gates), c_int(h.shape[0]),
+                             c_int(shared_ff), c_int(ff), c_int(E), c_int(MOE_ACT[act]), c_int(sm_count(h.device)),
+                             _stream())

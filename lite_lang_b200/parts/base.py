@@ -38,11 +38,18 @@ class TensorDecl:
     ``role`` decides how it is kept on the device and how random weights are
     drawn: ``matrix`` (compute dtype, N(0, s_matrix)), ``bias`` (float32,
     N(0, s_bias)), ``norm`` (float32, 1 + N(0, s_norm)), ``table`` (int32).
+    ``std`` replaces the role's standard deviation for this tensor (a mean of
+    ``mean``), for tensors whose useful range is not the role's.
+    A size given as None is one that only the checkpoint knows (the inner
+    width of a low-rank pair, say): any size fits, the part reads it off the
+    tensor in ``load``, and random weights cannot be drawn for it.
     """
 
-    shape: Tuple[int, ...]
+    shape: Tuple[Optional[int], ...]
     role: str = "matrix"
     optional: bool = False
+    std: Optional[float] = None
+    mean: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -104,8 +111,17 @@ class Norm(Part):
 
         The default is the unfused form; a part with a fused kernel overrides it.
         ``delta`` may also be float32 partial sums [parts, tokens, hidden] of a product that was
-        split over its inner dimension; they are added up first.
+        split over its inner dimension; they are added up first.  A block whose parts all read one
+        norm's output hands their outputs on as a tuple; they are added to each other first, then
+        to the residual.
         """
+        if isinstance(delta, (tuple, list)):
+            parts = [whole_output(d, residual.dtype).float() for d in delta if d is not None]
+            delta = None
+            if parts:
+                delta = parts[0]
+                for d in parts[1:]:
+                    delta = delta + d
         if delta is not None and delta.dim() == 3:
             delta = delta.sum(0).to(residual.dtype)
         if rows is not None:

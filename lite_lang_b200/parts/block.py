@@ -1,4 +1,6 @@
-"""Pre-norm arrangement: h += mixer(norm(h)); h += feed_forward(norm(h)).
+"""Arrangements of a layer's parts.
+
+Pre-norm: h += mixer(norm(h)); h += feed_forward(norm(h)).
 
 ``litelang/models/qwen2/layer/transformer_layer.py:46-77``.  The residual sums
 are folded into the norm that follows them (one pass over the row instead of
@@ -35,4 +37,30 @@ class PreNormBlock(Block):
         return h, f
 
 
+class ParallelBlock(Block):
+    """Parallel arrangement: with n = norm(h), h += mixer(n) + feed_forward(n).  One norm; both parts read
+    its output.  Their outputs are handed on together and added (to each other, then to the residual
+    stream) inside the next norm."""
+
+    roles = {"norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
+
+    def forward(self, h, delta, step, caches):
+        x = self.norm.add_forward(h, delta)
+        a = self.mixer.forward(x, step, caches["mixer"])
+        f = self.feed_forward.forward(x, step)
+        return h, (a, f)
+
+
+class ParallelMixerOnlyBlock(Block):
+    """The parallel arrangement of a layer without a feed-forward: h += mixer(norm(h))."""
+
+    roles = {"norm": "norm", "mixer": "mixer"}
+
+    def forward(self, h, delta, step, caches):
+        x = self.norm.add_forward(h, delta)
+        return h, self.mixer.forward(x, step, caches["mixer"])
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "parallel", ParallelBlock)
+register_part("block", "parallel_mixer_only", ParallelMixerOnlyBlock)

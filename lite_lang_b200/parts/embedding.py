@@ -23,15 +23,29 @@ class TokenEmbedding(Part):
         super().__init__(spec)
         self.vocab_size = int(spec.params["vocab_size"])
         self.hidden_size = int(spec.params["hidden_size"])
+        # ``scale``: a constant every row is multiplied by; ``residual``: "compute" (rows in the engine's
+        # dtype) or "float32" (a model whose residual stream stays in 32-bit); ``tensor``: the table's
+        # name under the prefix
+        self.scale = float(spec.params.get("scale", 1.0))
+        self.residual = str(spec.params.get("residual", "compute"))
+        self.tensor = str(spec.params.get("tensor", "weight"))
+        if self.residual not in ("compute", "float32"):
+            raise ValueError(f"token_embedding: residual {self.residual!r} is neither 'compute' nor 'float32'")
+        if self.residual == "compute" and self.scale != 1.0:
+            raise ValueError("token_embedding: a scale is built for a float32 residual stream only")
         self.weight: Optional[torch.Tensor] = None
 
     def tensors(self) -> Dict[str, TensorDecl]:
-        return {"weight": TensorDecl((self.vocab_size, self.hidden_size))}
+        return {self.tensor: TensorDecl((self.vocab_size, self.hidden_size))}
 
     def load(self, fetch, dtype, device) -> None:
-        self.weight = fetch("weight").to(dtype).to(device).contiguous()
+        self.weight = fetch(self.tensor).to(dtype).to(device).contiguous()
 
     def forward(self, token_ids: torch.Tensor, num_tokens: int, status) -> torch.Tensor:
+        if self.residual == "float32":
+            out = torch.empty((num_tokens, self.hidden_size), dtype=torch.float32, device=self.weight.device)
+            ops.embed_scaled_f32(out, self.weight, token_ids[:num_tokens], self.scale, status)
+            return out
         out = torch.empty((num_tokens, self.hidden_size), dtype=self.weight.dtype, device=self.weight.device)
         ops.embed_gather(out, self.weight, token_ids[:num_tokens], status)
         return out
@@ -45,15 +59,16 @@ class LMHead(Part):
         self.vocab_size = int(spec.params["vocab_size"])
         self.hidden_size = int(spec.params["hidden_size"])
         self.tied_to = spec.params.get("tied_to")
+        self.tensor = str(spec.params.get("tensor", "weight"))
         self.weight: Optional[torch.Tensor] = None
 
     def tensors(self) -> Dict[str, TensorDecl]:
         # With tied embeddings a checkpoint may or may not repeat the table under lm_head.
-        return {"weight": TensorDecl((self.vocab_size, self.hidden_size), optional=self.tied_to is not None)}
+        return {self.tensor: TensorDecl((self.vocab_size, self.hidden_size), optional=self.tied_to is not None)}
 
     def load(self, fetch, dtype, device) -> None:
         if self.tied_to is None:
-            self.weight = fetch("weight").to(dtype).to(device).contiguous()
+            self.weight = fetch(self.tensor).to(dtype).to(device).contiguous()
 
     def tie(self, table: torch.Tensor) -> None:
         self.weight = table

@@ -1,0 +1,110 @@
+"""Latent attention: keys and values expanded from one cached latent vector per token, sliding window.
+
+Per token the input is projected to ``heads`` queries, each [``dim`` plain | ``rot_dim`` rotated], and to
+``kv_rank + rot_dim`` numbers: the first ``kv_rank``, RMS-normed with a weight, are the latent c; the last
+``rot_dim`` are one rotated key part shared by all heads.  A head's plain key is Uk_h c, its value Uv_h c;
+score = (q_plain . k_plain + q_rot . k_rot) * ``scale``; position i sees j with 0 <= i - j < ``window``
+(None: every earlier position); softmax; output projection over the concatenated heads.
+
+Only c and the rotated key part are cached: ``kv_rank + rot_dim`` numbers a token in one plane of a paged
+group with one kv head and no value plane.  Nothing per head is expanded from the cache either: since
+q_plain . (Uk_h c) = (Uk_h^T q_plain) . c, the queries are taken into the latent space by a batched product
+over heads, attention runs there (keys: the cached rows; values: their first ``kv_rank`` numbers), and a
+second batched product expands each head's weighted sum of latents with Uv_h.
+
+Rotation: interleaved pairs (2i, 2i+1) of the rotated part's first ``rot_dims`` numbers turn by
+position * ``rot_base``^(-2i / rot_dims); the rest passes unchanged.  Angles (float32 position times a
+float32 frequency rounded from float64), the latent's norm, scores and softmax are float32.
+"""
+
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .. import ops
+from ..config.spec import PartSpec
+from .base import Mixer, PagedKVNeed, TensorDecl, register_part
+
+
+class LatentAttention(Mixer):
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.H = int(p["heads"])
+        self.d = int(p["dim"])
+        self.r = int(p["rot_dim"])
+        self.dv = int(p["vdim"])
+        self.R = int(p["kv_rank"])
+        self.window = None if p.get("window") is None else int(p["window"])
+        self.scale = float(p.get("scale", (self.d + self.r) ** -0.5))
+        self.rot_base = float(p.get("rot_base", 10000.0))
+        self.rot_dims = int(p.get("rot_dims", self.r))
+        self.eps = float(p["eps"])
+        if self.rot_dims % 2 or not (0 <= self.rot_dims <= self.r):
+            raise ValueError("latent_attention: rot_dims must be even and at most rot_dim")
+        if self.R > 512:
+            raise ValueError("latent_attention: a latent of more than 512 numbers is not built")
+        if self.window is not None and self.window <= 0:
+            raise ValueError("latent_attention: the window must be positive")
+        self.w_in = None
+
+    def tensors(self) -> Dict[str, TensorDecl]:
+        h = self.hidden_size
+        return {
+            "q": TensorDecl((self.H * (self.d + self.r), h)),
+            "dkv": TensorDecl((self.R + self.r, h)),
+            "dkv.norm": TensorDecl((self.R,), "norm"),
+            "uk": TensorDecl((self.H * self.d, self.R)),
+            "uv": TensorDecl((self.H * self.dv, self.R)),
+            "o": TensorDecl((h, self.H * self.dv)),
+        }
+
+    def load(self, fetch, dtype, device) -> None:
+        q = fetch("q").to(dtype)
+        self.kv_off = (q.shape[0] + 7) // 8 * 8
+        rows = [q]
+        if self.kv_off != q.shape[0]:
+            rows.append(torch.zeros((self.kv_off - q.shape[0], self.hidden_size), dtype=dtype))
+        rows.append(fetch("dkv").to(dtype))
+        self.w_in = torch.cat(rows, dim=0).to(device).contiguous()
+        self.norm_w = fetch("dkv.norm").to(torch.float32).to(device).contiguous()
+        self.w_uk = fetch("uk").to(dtype).to(device).contiguous().view(self.H, self.d, self.R)
+        self.w_uv_t = fetch("uv").to(dtype).to(device).contiguous().view(self.H, self.dv, self.R).transpose(1, 2)
+        self.w_o = fetch("o").to(dtype).to(device).contiguous()
+        i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
+        freq = self.rot_base ** (-2.0 * i / max(1, self.rot_dims))
+        self.freq = (freq.to(torch.float32) if freq.numel() else torch.zeros(1)).to(device).contiguous()
+
+    def weight_bytes(self) -> int:
+        ts = [self.w_in, self.w_uk, self.w_uv_t, self.w_o]
+        return sum(t.numel() * t.element_size() for t in ts)
+
+    def cache_need(self):
+        return PagedKVNeed(1, self.R + self.r, self.window, value_head_dim=0)
+
+    def kernel_libraries(self):
+        libs = ["core", "latent_attn"]
+        if self.w_in is not None and self.w_in.dtype == torch.bfloat16:
+            libs.extend(["gemm_smallm", "gemm_stream", "gemm_tc"])
+        return libs
+
+    def forward(self, x, step, cache):
+        n, dev, H, d, r, R = x.shape[0], x.device, self.H, self.d, self.r, self.R
+        proj = ops.linear(x, self.w_in)
+        q_rot = torch.empty((n, H, r), dtype=torch.float32, device=dev)
+        ops.latent_prepare(proj, 0, self.kv_off, self.norm_w, self.eps, self.freq, self.rot_dims, step.positions,
+                           cache.slot_map if cache.writable else None, cache.k, q_rot, H, d, r, R, step.status)
+        q_plain = proj[:, :H * (d + r)].view(n, H, d + r)[:, :, :d].permute(1, 0, 2)          # [H, n, d]
+        qa = ops.batched_heads(q_plain, self.w_uk, out_dtype=torch.float32)                     # [H, n, R]
+        lat = torch.empty((H, n, R), dtype=x.dtype, device=dev)
+        ops.latent_attention(lat, qa, q_rot, cache.k, cache.block_table, step, H, R, r, cache.page_size,
+                             self.window, self.scale)
+        heads = torch.empty((n, H * self.dv), dtype=x.dtype, device=dev)
+        ops.batched_heads(lat, self.w_uv_t, out=heads.view(n, H, self.dv).permute(1, 0, 2))
+        return ops.linear(heads, self.w_o)
+
+
+register_part("mixer", "latent_attention", LatentAttention)

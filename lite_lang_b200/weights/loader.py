@@ -68,8 +68,11 @@ def check_against(declared: Mapping[str, object], shapes: Mapping[str, Tuple[int
     """Raise one WeightError that lists missing, unexpected and wrongly shaped tensors."""
     missing = [n for n, d in declared.items() if n not in shapes and not d.optional]
     unexpected = [n for n in shapes if n not in declared]
+    def fits(want, have) -> bool:      # a declared size of None is one that only the checkpoint knows
+        return len(want) == len(have) and all(w is None or w == h for w, h in zip(want, have))
+
     wrong = [(n, tuple(d.shape), tuple(shapes[n])) for n, d in declared.items()
-             if n in shapes and tuple(shapes[n]) != tuple(d.shape)]
+             if n in shapes and not fits(tuple(d.shape), tuple(shapes[n]))]
     if not (missing or unexpected or wrong):
         return
     lines = [f"the weights in {where} do not fit the model:"]

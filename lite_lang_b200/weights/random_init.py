@@ -26,7 +26,12 @@ def draw_tensor(name: str, decl, seed: int, scales: Mapping[str, float], dtype: 
     gen = torch.Generator(device=device)
     gen.manual_seed((int(seed) * 1000003 + zlib.crc32(name.encode())) % (2 ** 63))
     shape = tuple(decl.shape)
-    if decl.role == "norm":
+    if any(n is None for n in shape):
+        raise ValueError(f"tensor {name}: a size that only a checkpoint gives; name it in the configuration "
+                         "to draw random weights")
+    if getattr(decl, "std", None) is not None and decl.role != "table":
+        t = decl.mean + decl.std * torch.randn(shape, generator=gen, dtype=torch.float32, device=device)
+    elif decl.role == "norm":
         t = 1.0 + scales["norm"] * torch.randn(shape, generator=gen, dtype=torch.float32, device=device)
     elif decl.role == "bias":
         t = scales["bias"] * torch.randn(shape, generator=gen, dtype=torch.float32, device=device)
