@@ -107,7 +107,8 @@ class TraceRun:
         self.proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=self._err,
                                      text=True, bufsize=1, env=env)
         self.step_no = 0
-        self.vocab = json.load(open(os.path.join(model_dir, "config.json")))["vocab_size"]
+        cfg = json.load(open(os.path.join(model_dir, "config.json")))
+        self.vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
 
     def step(self, entries: Sequence[dict], end: Sequence[str] = ()) -> Optional[np.ndarray]:
         """entries: [{"id", "tokens", "want"}].  Returns the wanted logits [wanted, vocab] or None."""
