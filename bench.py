@@ -456,6 +456,115 @@ def run_ours(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------------
+# --compare nevurax: the Nevurax design beside Qwen2 at equal layer sizes (random weights)
+# ---------------------------------------------------------------------------------------------------------
+def _nevurax_shape(width, heads, kv_heads, head, inter, vocab, layers, window, experts, top):
+    """A Nevurax model whose layers are as large as a Qwen2 layer of the given sizes: the mixers have as many
+    heads of the same size (the latent is four key heads wide), the routed feed-forward has as many *active*
+    weights as the gated one (two matrices instead of three: top experts + the shared one = 1.5 x inter hidden
+    units) and experts / top times as many in all."""
+    ff = (3 * inter // 2) // (top + 1) // 64 * 64
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}, "shared": {"ff": ff}}
+    latent = {"heads": heads, "dim": head - 32, "rot_dim": 32, "vdim": head, "kv_rank": 4 * head,
+              "mask": {"size": window}, "rot": {"base": 1e6, "dims": 32}, "scale": head ** -0.5}
+    delta = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "conv": 4}
+    cdelta = dict(delta, decay_rank=64, gate_rank=64)
+    kinds = [("delta", delta), ("latent_attention", latent), ("channel_delta", cdelta), ("latent_attention", latent)]
+    return {"architecture": "Nevurax", "vocab": vocab, "width": width, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6},
+            "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": moe} for i in range(layers)]}
+
+
+COMPARE_SIZES = {
+    # name: (Qwen2 sizes, window of the latent attention, experts, top)
+    "1p5b": (dict(QWEN2_1P5B, vocab_size=32768), 512, 16, 4),
+    "7b": (dict(architectures=["Qwen2ForCausalLM"], hidden_size=3584, num_attention_heads=28, num_key_value_heads=4,
+                intermediate_size=18944, vocab_size=32768, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                tie_word_embeddings=False, max_position_embeddings=32768, use_sliding_window=False,
+                torch_dtype="bfloat16"), 1024, 8, 2),
+}
+
+
+def _kernel_table(engine, entries_fn, steps=3):
+    """Device time of every kernel of a step, by name, from torch.profiler (microseconds a step)."""
+    import collections
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    entries_fn()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            entries_fn()
+        torch.cuda.synchronize()
+    agg = collections.OrderedDict()
+    for e in prof.events():
+        if e.device_type == torch.autograd.DeviceType.CUDA:
+            a = agg.setdefault(e.name[:60], [0, 0.0])
+            a[0] += 1
+            a[1] += e.device_time
+    return [{"kernel": k, "calls": round(n / steps, 1), "us": round(t / steps, 1)}
+            for k, (n, t) in sorted(agg.items(), key=lambda kv: -kv[1][1])][:14]
+
+
+def run_compare(args):
+    """Prefill (2,048 tokens) and decode (batch 8 and 64 at context 2,048) of a few layers of both designs."""
+    import torch
+    from lite_lang_b200.engine.batch import StepEntry
+    pk = peaks()
+    layers = args.layers or 4
+    out = {"compare": "nevurax", "layers": layers, "dtype": "bfloat16", "data": "synthetic", "peaks": pk, "sizes": {}}
+    for name, (qwen, window, experts, top) in COMPARE_SIZES.items():
+        if args.shape_name and args.shape_name != name:
+            continue
+        row = {}
+        nev = _nevurax_shape(qwen["hidden_size"], qwen["num_attention_heads"], qwen["num_key_value_heads"],
+                             qwen["hidden_size"] // qwen["num_attention_heads"], qwen["intermediate_size"],
+                             qwen["vocab_size"], layers, window, experts, top)
+        for design, model in (("qwen2", qwen), ("nevurax", nev)):
+            engine = build_engine(layers, 64, model=model)
+            r = {"weight_bytes": engine.model.weight_bytes_per_step()}
+            pre = prefill_once(engine, repeats=10, seconds=0.3)
+            r["prefill_ms"] = round(pre["ms"], 3)
+            r["prefill_tok_s"] = round(PROMPT_LEN / pre["ms"] * 1e3, 1)
+            for b in (8, 64):
+                ms, _ = device_decode(engine, b, max(16, args.steps // 4), max(3, args.warmup))
+                r[f"decode_b{b}_ms"] = round(ms, 4)
+                r[f"decode_b{b}_tok_s"] = round(b / ms * 1e3, 1)
+            if args.kernels:
+                m, runner = engine.manager, engine.runner
+                prompt = random_prompts(1, PROMPT_LEN, engine.model.spec.vocab_size, 11)[0]
+
+                def prefill_step():
+                    s = m.open()
+                    assert runner.reserve(s, PROMPT_LEN)
+                    runner.step([StepEntry(s, prompt, (PROMPT_LEN - 1,))])
+                    m.close(s)
+                r["prefill_kernels"] = _kernel_table(engine, prefill_step)
+                slots = []
+                for p in random_prompts(8, PROMPT_LEN, engine.model.spec.vocab_size, 7):
+                    s = m.open()
+                    assert runner.reserve(s, PROMPT_LEN)
+                    runner.step([StepEntry(s, p, ())])
+                    slots.append(s)
+
+                def decode_step():
+                    for s in slots:
+                        assert runner.reserve(s, 1)
+                    runner.step([StepEntry(s, [7], (0,)) for s in slots], allow_graph=False)
+                r["decode_b8_kernels"] = _kernel_table(engine, decode_step)
+                for s in slots:
+                    m.close(s)
+            row[design] = r
+            del engine
+            torch.cuda.empty_cache()
+        row["config"] = {"nevurax": {"window": window, "experts": experts, "top": top,
+                                     "expert_ff": nev["layers"][0]["mlp"]["expert"]["ff"]}}
+        out["sizes"][name] = row
+    print(json.dumps(out))
+    return 0
+
+
 def run_reference(args):
     """The unmodified reference from baseline/_ref through its own runner API, if it is installed."""
     ref = os.path.join(ROOT, "baseline", "_ref")
@@ -558,6 +667,12 @@ def main():
                     help="with --only decode: another context length than the headline's 2,048 prompt tokens")
     ap.add_argument("--shape", default="", choices=[""] + sorted(WORKLOADS),
                     help="with --only: the layer sizes of that workload's model instead of Qwen2-1.5B's")
+    ap.add_argument("--compare", default="", choices=["", "nevurax"],
+                    help="instead of the headline measurement: prefill and decode of a few layers of that design beside "
+                         "Qwen2 at equal layer sizes (random weights); --layers (default 4), --size, --kernels go with it")
+    ap.add_argument("--size", default="", dest="shape_name", choices=[""] + sorted(COMPARE_SIZES),
+                    help="with --compare: only that size")
+    ap.add_argument("--kernels", action="store_true", help="with --compare: also every step's kernels by name")
     args = ap.parse_args()
     if args.shape and not args.only:
         ap.error("--shape goes with --only (the headline measurement is of the Qwen2-1.5B sizes)")
@@ -576,6 +691,8 @@ def main():
         return run_reference(args)
     if args.workload:
         return run_workload(args)
+    if args.compare:
+        return run_compare(args)
     return run_ours(args)
 
 

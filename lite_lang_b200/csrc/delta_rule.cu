@@ -132,9 +132,12 @@ __global__ void delta_conv_update_kernel(const T* __restrict__ proj, long proj_s
 
 // The scan.  A block of 128 threads owns 16 value columns of one (entry, head); 8 lanes share a column, lane l
 // holding key channels l, l + 8, ... in NR registers.  q, k (and a per-channel decay) of a token go through
-// shared memory, filled one token ahead.
+// shared memory, double-buffered: the next token's numbers are asked for (into registers) before the current
+// token is worked on and put into the other buffer after it, so that their way from memory lies under the
+// arithmetic.  Sums run in two interleaved chains (even and odd registers) in a fixed order.
 #define DR_COLS 16
 #define DR_LANES 8
+#define DR_NF 2      // shared-memory numbers a thread fetches per token and array: covers dk <= 256
 template <int NR>
 __global__ void __launch_bounds__(DR_COLS * DR_LANES)
 delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vc,
@@ -158,6 +161,7 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
   }
   const int hk = h / (s.H / s.Hk);
   const int ng = s.per_channel ? s.H * dk : s.H;
+  const bool pc = s.per_channel != 0;
   float* S_ptr = state + (size_t)slot * state_stride + (size_t)h * dk * s.dv;
   float S[NR];
 #pragma unroll
@@ -165,51 +169,81 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
     const int c = l + DR_LANES * i;
     S[i] = (live_col && c < dk) ? S_ptr[(size_t)c * s.dv + col] : 0.f;
   }
-  auto fill = [&](int t, int buf) {
+  // what this thread brings of a token: up to DR_NF numbers of q, k and the decay, and its own v, beta, decay
+  float fq[DR_NF], fk[DR_NF], fg[DR_NF], fv = 0.f, fb = 0.f, fgh = 1.f;
+  auto fetch = [&](int t) {
+#pragma unroll
+    for (int u = 0; u < DR_NF; ++u) {
+      const int i = tid + u * DR_COLS * DR_LANES;
+      if (i < dk) {
+        fq[u] = qn[(size_t)t * Cq + (size_t)hk * dk + i];
+        fk[u] = kn[(size_t)t * Cq + (size_t)hk * dk + i];
+        if (pc) fg[u] = g[(size_t)t * ng + (size_t)h * dk + i];
+      }
+    }
+    fv = live_col ? vc[(size_t)t * Cv + (size_t)h * s.dv + col] : 0.f;
+    fb = beta[(size_t)t * s.H + h];
+    if (!pc) fgh = g[(size_t)t * ng + h];
+  };
+  auto put = [&](int buf) {
     float* b = sm + (size_t)buf * 3 * dk;
-    for (int i = tid; i < dk; i += blockDim.x) {
-      b[i] = qn[(size_t)t * Cq + (size_t)hk * dk + i];
-      b[dk + i] = kn[(size_t)t * Cq + (size_t)hk * dk + i];
-      if (s.per_channel) b[2 * dk + i] = g[(size_t)t * ng + (size_t)h * dk + i];
+#pragma unroll
+    for (int u = 0; u < DR_NF; ++u) {
+      const int i = tid + u * DR_COLS * DR_LANES;
+      if (i < dk) {
+        b[i] = fq[u];
+        b[dk + i] = fk[u];
+        if (pc) b[2 * dk + i] = fg[u];
+      }
     }
   };
-  if (first < last) fill(first, 0);
+  float v = 0.f, b = 0.f, gh = 1.f;
+  if (first < last) {
+    fetch(first);
+    put(0);
+    v = fv, b = fb, gh = fgh;
+  }
   __syncthreads();
   for (int t = first; t < last; ++t) {
     const int buf = (t - first) & 1;
-    if (t + 1 < last) fill(t + 1, buf ^ 1);
+    if (t + 1 < last) fetch(t + 1);
     const float* sq = sm + (size_t)buf * 3 * dk;
     const float* sk = sq + dk;
     const float* sg = sk + dk;
-    const float gh = s.per_channel ? 1.f : g[(size_t)t * ng + h];
-    const float b = beta[(size_t)t * s.H + h];
-    const float v = live_col ? vc[(size_t)t * Cv + (size_t)h * s.dv + col] : 0.f;
-    float dot = 0.f;
+    float kr[NR];
+    float d0 = 0.f, d1 = 0.f;
 #pragma unroll
     for (int i = 0; i < NR; ++i) {
       const int c = l + DR_LANES * i;
-      if (c < dk) {
-        S[i] *= s.per_channel ? sg[c] : gh;
-        dot = fmaf(S[i], sk[c], dot);
-      }
+      kr[i] = c < dk ? sk[c] : 0.f;
+      const float dec = pc ? (c < dk ? sg[c] : 1.f) : gh;
+      S[i] *= dec;
+      if (i & 1) d1 = fmaf(S[i], kr[i], d1);
+      else d0 = fmaf(S[i], kr[i], d0);
     }
+    float dot = d0 + d1;
     dot += __shfl_xor_sync(0xffffffffu, dot, 1);
     dot += __shfl_xor_sync(0xffffffffu, dot, 2);
     dot += __shfl_xor_sync(0xffffffffu, dot, 4);
     const float u = b * (v - dot);
-    float oq = 0.f;
+    float o0 = 0.f, o1 = 0.f;
 #pragma unroll
     for (int i = 0; i < NR; ++i) {
       const int c = l + DR_LANES * i;
-      if (c < dk) {
-        S[i] = fmaf(sk[c], u, S[i]);
-        oq = fmaf(S[i], sq[c], oq);
-      }
+      const float qv = c < dk ? sq[c] : 0.f;
+      S[i] = fmaf(kr[i], u, S[i]);
+      if (i & 1) o1 = fmaf(S[i], qv, o1);
+      else o0 = fmaf(S[i], qv, o0);
     }
+    float oq = o0 + o1;
     oq += __shfl_xor_sync(0xffffffffu, oq, 1);
     oq += __shfl_xor_sync(0xffffffffu, oq, 2);
     oq += __shfl_xor_sync(0xffffffffu, oq, 4);
     if (live_col && l == 0) o[(size_t)t * Cv + (size_t)h * s.dv + col] = oq;
+    if (t + 1 < last) {
+      put(buf ^ 1);
+      v = fv, b = fb, gh = fgh;
+    }
     __syncthreads();
   }
 #pragma unroll

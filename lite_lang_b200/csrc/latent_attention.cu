@@ -15,8 +15,12 @@
 //   latent_prepare    per token: RMS norm of the latent, rotation of k_r and of every head's q_r, cache write
 //   latent_attention  per (token, 8 heads): online softmax over the visible rows of the request, i.e.
 //                     positions lo..p with lo = max(0, p - window + 1) (window <= 0: all)
-// Keys are walked in tiles of 32 positions that start at multiples of 32, so the order of every sum depends
-// on the position only, not on how the tokens were cut into steps or batched.
+//   latent_gather, latent_masked_softmax: the pieces between two library products for long prompt portions,
+//                     where all (token, head) rows of a block of queries meet the same run of cached rows:
+//                     the run is copied out of its pages, scores = Q K^T and sum = P C are products, and the
+//                     masked softmax between them is the kernel here
+// In latent_attention keys are walked in tiles of 32 positions that start at multiples of 32, so the order of
+// every sum depends on the position only, not on how the tokens were cut into steps or batched.
 #include "common.cuh"
 
 // proj row t: q heads at q_off, head h's rotated part at q_off + h * (d + r) + d; the latent at kv_off (R wide),
@@ -26,14 +30,14 @@ __global__ void __launch_bounds__(128)
 latent_prepare_kernel(const T* __restrict__ proj, long proj_stride, int q_off, int kv_off, const float* __restrict__ norm_w,
                       float eps, const float* __restrict__ freq, int rot_dims, const int* __restrict__ positions,
                       const int* __restrict__ slot_map, T* __restrict__ cache, long num_slots,
-                      float* __restrict__ q_rot, int H, int d, int r, int R, int* status) {
+                      T* __restrict__ q_full, int H, int d, int r, int R, int* status) {
   __shared__ float scratch[32];
   LL_PDL_TRIGGER();
   LL_PDL_WAIT();
   const int t = blockIdx.x, tid = threadIdx.x;
   const T* row = proj + (size_t)t * proj_stride;
   const float p = (float)positions[t];
-  // every head's rotated query part -> float32 [tokens, H, r]
+  // every head's rotated query part -> q_full [tokens, H, R + r] behind the R latent-space numbers
   const int half = rot_dims / 2;
   for (int i = tid; i < H * r; i += blockDim.x) {
     const int h = i / r, j = i % r;
@@ -47,7 +51,7 @@ latent_prepare_kernel(const T* __restrict__ proj, long proj_stride, int q_off, i
     } else {
       out = to_f32<T>(src[j]);
     }
-    q_rot[((size_t)t * H + h) * r + j] = out;
+    q_full[((size_t)t * H + h) * (R + r) + R + j] = from_f32<T>(out);
   }
   const long slot = slot_map ? slot_map[t] : -1;
   if (slot < 0) return;     // padding token, or a run-step that only reads this plane
@@ -85,46 +89,42 @@ latent_prepare_kernel(const T* __restrict__ proj, long proj_stride, int q_off, i
 #define LA_GH 8
 #define LA_MAX_R 512
 
-// qa: float32 latent-space queries, head h of token t at qa + h * qa_hstride + t * qa_tstride (R numbers);
-// q_rot: float32 [tokens, H, r]; cache: one plane [pages, 1, page_size, R + r]; out: T, head h of token t at
-// out + h * out_hstride + t * out_tstride (R numbers).
+// q: [tokens, H, R + r] of T (latent-space queries, then the rotated part); cache: one plane
+// [pages, 1, page_size, R + r]; out: [tokens, H, R] of T.  `first` is the first token of the launch.
 template <typename T>
 __global__ void __launch_bounds__(LA_THREADS)
-latent_attention_kernel(T* __restrict__ out, long out_hstride, long out_tstride, const float* __restrict__ qa,
-                        long qa_hstride, long qa_tstride, const float* __restrict__ q_rot,
-                        const T* __restrict__ cache, const int* __restrict__ block_table, int bt_stride,
-                        const int* __restrict__ token_req, const int* __restrict__ req_slot,
-                        const int* __restrict__ positions, int H, int R, int r, int page_size, int num_pages,
-                        int window, float scale, int* status) {
+latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ cache,
+                        const int* __restrict__ block_table, int bt_stride, const int* __restrict__ token_req,
+                        const int* __restrict__ req_slot, const int* __restrict__ positions, int first, int H, int R,
+                        int r, int page_size, int num_pages, int window, float scale, int* status) {
   extern __shared__ float smem[];
+  __shared__ long base_s[LA_TK];
   LL_PDL_TRIGGER();
   LL_PDL_WAIT();
-  const int t = blockIdx.x;
+  const int t = first + blockIdx.x;
   const int h0 = blockIdx.y * LA_GH;
   const int hc = min(LA_GH, H - h0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int KD = R + r;
   float* qs = smem;                         // [LA_GH][KD]
   float* ks = qs + LA_GH * KD;              // [LA_TK][KD + 1]
-  float* ps = ks + LA_TK * (KD + 1);        // [LA_GH][LA_TK]
+  float* ps = ks + LA_TK * (KD + 1);        // [LA_TK][LA_GH]
   float* alpha_s = ps + LA_GH * LA_TK;      // [LA_GH]
   float* l_s = alpha_s + LA_GH;             // [LA_GH]
 
   const int entry = token_req[t];
   const int slot = entry >= 0 ? req_slot[entry] : -1;
   const int p = positions[t];
+  T* o_row = out + ((size_t)t * H + h0) * R;
   if (slot < 0 || p < 0) {
-    for (int i = tid; i < hc * R; i += LA_THREADS)
-      out[(size_t)(h0 + i / R) * out_hstride + (size_t)t * out_tstride + i % R] = from_f32<T>(0.f);
+    for (int i = tid; i < hc * R; i += LA_THREADS) o_row[i] = from_f32<T>(0.f);
     return;
   }
   const int* bt = block_table + (size_t)slot * bt_stride;
   const int lo = (window > 0) ? max(0, p - window + 1) : 0;
-  for (int i = tid; i < hc * KD; i += LA_THREADS) {
-    const int g = i / KD, j = i % KD;
-    qs[i] = j < R ? qa[(size_t)(h0 + g) * qa_hstride + (size_t)t * qa_tstride + j]
-                  : q_rot[((size_t)t * H + h0 + g) * r + (j - R)];
-  }
+  const T* q_row = q + ((size_t)t * H + h0) * KD;
+  for (int i = tid; i < hc * KD; i += LA_THREADS) qs[i] = to_f32<T>(q_row[i]);
+  for (int i = hc * KD + tid; i < LA_GH * KD; i += LA_THREADS) qs[i] = 0.f;
   float m_run[LA_GH / LA_WARPS], l_run[LA_GH / LA_WARPS];
 #pragma unroll
   for (int i = 0; i < LA_GH / LA_WARPS; ++i) {
@@ -136,60 +136,120 @@ latent_attention_kernel(T* __restrict__ out, long out_hstride, long out_tstride,
   for (int g = 0; g < LA_GH; ++g)
 #pragma unroll
     for (int c = 0; c < LA_MAX_R / LA_THREADS; ++c) acc[g][c] = 0.f;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const bool vec_ok = (KD % VEC) == 0 && ((uintptr_t)cache % 16) == 0;
 
   for (int tile0 = (lo / LA_TK) * LA_TK; tile0 <= p; tile0 += LA_TK) {
     __syncthreads();
-    for (int j = warp; j < LA_TK; j += LA_WARPS) {
-      const int pos = tile0 + j;
-      const bool valid = (pos >= lo && pos <= p);
+    if (tid < LA_TK) {
+      const int pos = tile0 + tid;
       long base = -1;
-      if (valid) {
+      if (pos >= lo && pos <= p) {
         const int page = bt[pos / page_size];
-        if (page < 0 || page >= num_pages) {
-          if (lane == 0) set_status(status, LL_ERR_PAGE_RANGE);
-        } else {
-          base = ((long)page * page_size + (pos % page_size)) * KD;
+        if (page < 0 || page >= num_pages) set_status(status, LL_ERR_PAGE_RANGE);
+        else base = ((long)page * page_size + (pos % page_size)) * KD;
+      }
+      base_s[tid] = base;
+    }
+    __syncthreads();
+    // the tile's rows: every thread asks for four pieces before it uses the first
+    if (vec_ok) {
+      const int vpr = KD / VEC, total = LA_TK * vpr;
+      for (int i0 = tid; i0 < total; i0 += LA_THREADS * 4) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u * LA_THREADS;
+          v[u] = make_uint4(0, 0, 0, 0);
+          if (i < total) {
+            const long base = base_s[i / vpr];
+            if (base >= 0) v[u] = *reinterpret_cast<const uint4*>(cache + base + (size_t)(i % vpr) * VEC);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u * LA_THREADS;
+          if (i < total) {
+            const T* e = reinterpret_cast<const T*>(&v[u]);
+            float* dst = ks + (i / vpr) * (KD + 1) + (i % vpr) * VEC;
+#pragma unroll
+            for (int x = 0; x < VEC; ++x) dst[x] = to_f32<T>(e[x]);
+          }
         }
       }
-      for (int c = lane; c < KD; c += 32) ks[j * (KD + 1) + c] = base >= 0 ? to_f32<T>(cache[base + c]) : 0.f;
+    } else {
+      const int total = LA_TK * KD;
+      for (int i0 = tid; i0 < total; i0 += LA_THREADS * 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = i0 + u * LA_THREADS;
+          v[u] = 0.f;
+          if (i < total) {
+            const long base = base_s[i / KD];
+            if (base >= 0) v[u] = to_f32<T>(cache[base + i % KD]);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = i0 + u * LA_THREADS;
+          if (i < total) ks[(i / KD) * (KD + 1) + i % KD] = v[u];
+        }
+      }
     }
     __syncthreads();
     {
+      // scores and online softmax: warp w owns heads w and w + 4; lane = key
       const int pos = tile0 + lane;
       const bool valid = (pos >= lo && pos <= p);
+      float s0 = 0.f, s1 = 0.f;
+      const float* q0 = qs + warp * KD;
+      const float* q1 = qs + (warp + LA_WARPS) * KD;
+      const float* kj = ks + lane * (KD + 1);
+      for (int c = 0; c < KD; ++c) {
+        const float kv = kj[c];
+        s0 = fmaf(q0[c], kv, s0);
+        s1 = fmaf(q1[c], kv, s1);
+      }
 #pragma unroll
       for (int i = 0; i < LA_GH / LA_WARPS; ++i) {
         const int g = warp + i * LA_WARPS;
         if (g < hc) {
-          float s = 0.f;
-          const float* qg = qs + g * KD;
-          const float* kj = ks + lane * (KD + 1);
-          for (int c = 0; c < KD; ++c) s = fmaf(qg[c], kj[c], s);
-          s = valid ? s * scale : -INFINITY;
+          const float s = valid ? (i == 0 ? s0 : s1) * scale : -INFINITY;
           const float m_new = fmaxf(m_run[i], warp_max(s));
           const float pj = valid ? expf(s - m_new) : 0.f;
           const float alpha = expf(m_run[i] - m_new);
           l_run[i] = l_run[i] * alpha + warp_sum(pj);
           m_run[i] = m_new;
-          ps[g * LA_TK + lane] = pj;
+          ps[lane * LA_GH + g] = pj;
           if (lane == 0) alpha_s[g] = alpha;
+        } else {
+          ps[lane * LA_GH + g] = 0.f;
+          if (lane == 0) alpha_s[g] = 1.f;
         }
       }
     }
     __syncthreads();
+    // accumulate P C: thread owns latent columns tid, tid + 128, ...; a key's number is read once for all heads
 #pragma unroll
     for (int c = 0; c < LA_MAX_R / LA_THREADS; ++c) {
       const int dd = tid + c * LA_THREADS;
       if (dd < R) {
 #pragma unroll
-        for (int g = 0; g < LA_GH; ++g) {
-          if (g < hc) {
-            float a = acc[g][c] * alpha_s[g];
-            const float* pg = ps + g * LA_TK;
-#pragma unroll 8
-            for (int j = 0; j < LA_TK; ++j) a = fmaf(pg[j], ks[j * (KD + 1) + dd], a);
-            acc[g][c] = a;
-          }
+        for (int g = 0; g < LA_GH; ++g) acc[g][c] *= alpha_s[g];
+#pragma unroll 4
+        for (int j = 0; j < LA_TK; ++j) {
+          const float kv = ks[j * (KD + 1) + dd];
+          const float4 pa = *reinterpret_cast<const float4*>(ps + j * LA_GH);
+          const float4 pb = *reinterpret_cast<const float4*>(ps + j * LA_GH + 4);
+          acc[0][c] = fmaf(pa.x, kv, acc[0][c]);
+          acc[1][c] = fmaf(pa.y, kv, acc[1][c]);
+          acc[2][c] = fmaf(pa.z, kv, acc[2][c]);
+          acc[3][c] = fmaf(pa.w, kv, acc[3][c]);
+          acc[4][c] = fmaf(pb.x, kv, acc[4][c]);
+          acc[5][c] = fmaf(pb.y, kv, acc[5][c]);
+          acc[6][c] = fmaf(pb.z, kv, acc[6][c]);
+          acc[7][c] = fmaf(pb.w, kv, acc[7][c]);
         }
       }
     }
@@ -206,29 +266,69 @@ latent_attention_kernel(T* __restrict__ out, long out_hstride, long out_tstride,
     if (dd < R) {
 #pragma unroll
       for (int g = 0; g < LA_GH; ++g)
-        if (g < hc)
-          out[(size_t)(h0 + g) * out_hstride + (size_t)t * out_tstride + dd] = from_f32<T>(acc[g][c] / l_s[g]);
+        if (g < hc) o_row[(size_t)g * R + dd] = from_f32<T>(acc[g][c] / l_s[g]);
     }
   }
 }
 
+// Rows lo .. lo + n - 1 of a request's cached rows, copied out of their pages into dst [n, KD].
+template <typename T>
+__global__ void latent_gather_kernel(T* __restrict__ dst, const T* __restrict__ cache, const int* __restrict__ bt,
+                                     int lo, int n, int KD, int page_size, int num_pages, int* status) {
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  for (int j = blockIdx.x; j < n; j += gridDim.x) {
+    const int pos = lo + j;
+    const int page = bt[pos / page_size];
+    const bool ok = page >= 0 && page < num_pages;
+    if (!ok && threadIdx.x == 0) set_status(status, LL_ERR_PAGE_RANGE);
+    const T* src = cache + ((size_t)(ok ? page : 0) * page_size + (pos % page_size)) * KD;
+    for (int c = threadIdx.x; c < KD; c += blockDim.x) dst[(size_t)j * KD + c] = ok ? src[c] : from_f32<T>(0.f);
+  }
+}
+
+// Row i = (query token i / H of the block, head i % H): scores S [rows, n_keys] float32, key column j is
+// position lo + j; the query's position is p0 + i / H and it sees columns with
+// max(lo, p - window + 1) <= lo + j <= p.  P = softmax(scale * S) over those, zero elsewhere, in T.
+template <typename T>
+__global__ void __launch_bounds__(256)
+latent_masked_softmax_kernel(T* __restrict__ P, const float* __restrict__ S, int rows, int n_keys, int H, int p0, int lo,
+                             int window, float scale) {
+  __shared__ float scratch[32];
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const int i = blockIdx.x;
+  const int p = p0 + i / H;
+  const int first = (window > 0 ? max(lo, p - window + 1) : lo) - lo, last = p - lo;   // visible columns, inclusive
+  const float* s = S + (size_t)i * n_keys;
+  T* out = P + (size_t)i * n_keys;
+  float m = -INFINITY;
+  for (int j = first + threadIdx.x; j <= last; j += blockDim.x) m = fmaxf(m, s[j] * scale);
+  m = block_max(m, scratch);
+  float sum = 0.f;
+  for (int j = first + threadIdx.x; j <= last; j += blockDim.x) sum += expf(s[j] * scale - m);
+  sum = block_sum(sum, scratch);
+  const float inv = 1.0f / sum;
+  for (int j = threadIdx.x; j < n_keys; j += blockDim.x)
+    out[j] = from_f32<T>((j >= first && j <= last) ? expf(s[j] * scale - m) * inv : 0.f);
+}
+
 extern "C" int ll_latent_prepare(int dtype, const void* proj, long proj_stride, int q_off, int kv_off,
                                  const float* norm_w, float eps, const float* freq, int rot_dims, const int* positions,
-                                 const int* slot_map, void* cache, long num_slots, float* q_rot, int num_tokens, int H,
+                                 const int* slot_map, void* cache, long num_slots, void* q_full, int num_tokens, int H,
                                  int d, int r, int R, int* status, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (H <= 0 || d < 0 || r < 0 || R <= 0 || rot_dims < 0 || rot_dims > r) return (int)cudaErrorInvalidValue;
   LL_DISPATCH_DTYPE(dtype, ll_launch(latent_prepare_kernel<T>, dim3(num_tokens), dim3(128), 0, stream, (const T*)proj,
                                      proj_stride, q_off, kv_off, norm_w, eps, freq, rot_dims, positions, slot_map,
-                                     (T*)cache, num_slots, q_rot, H, d, r, R, status));
+                                     (T*)cache, num_slots, (T*)q_full, H, d, r, R, status));
   return LL_LAUNCH_RESULT();
 }
 
-extern "C" int ll_latent_attention(int dtype, void* out, long out_hstride, long out_tstride, const float* qa,
-                                   long qa_hstride, long qa_tstride, const float* q_rot, const void* cache,
-                                   const int* block_table, int bt_stride, const int* token_req, const int* req_slot,
-                                   const int* positions, int num_tokens, int H, int R, int r, int page_size,
-                                   int num_pages, int window, float scale, int* status, cudaStream_t stream) {
+extern "C" int ll_latent_attention(int dtype, void* out, const void* q, const void* cache, const int* block_table,
+                                   int bt_stride, const int* token_req, const int* req_slot, const int* positions,
+                                   int first, int num_tokens, int H, int R, int r, int page_size, int num_pages,
+                                   int window, float scale, int* status, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (H <= 0 || R <= 0 || R > LA_MAX_R || r < 0 || page_size <= 0) return (int)cudaErrorInvalidValue;
   const int KD = R + r;
@@ -237,9 +337,25 @@ extern "C" int ll_latent_attention(int dtype, void* out, long out_hstride, long 
   LL_DISPATCH_DTYPE(dtype, {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(latent_attention_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    ll_launch(latent_attention_kernel<T>, grid, dim3(LA_THREADS), smem, stream, (T*)out, out_hstride, out_tstride, qa,
-              qa_hstride, qa_tstride, q_rot, (const T*)cache, block_table, bt_stride, token_req, req_slot, positions, H,
-              R, r, page_size, num_pages, window, scale, status);
+    ll_launch(latent_attention_kernel<T>, grid, dim3(LA_THREADS), smem, stream, (T*)out, (const T*)q, (const T*)cache,
+              block_table, bt_stride, token_req, req_slot, positions, first, H, R, r, page_size, num_pages, window,
+              scale, status);
   });
+  return LL_LAUNCH_RESULT();
+}
+
+extern "C" int ll_latent_gather(int dtype, void* dst, const void* cache, const int* bt_row, int lo, int n, int KD,
+                                int page_size, int num_pages, int* status, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  LL_DISPATCH_DTYPE(dtype, ll_launch(latent_gather_kernel<T>, dim3(n < 1024 ? n : 1024), dim3(128), 0, stream, (T*)dst,
+                                     (const T*)cache, bt_row, lo, n, KD, page_size, num_pages, status));
+  return LL_LAUNCH_RESULT();
+}
+
+extern "C" int ll_latent_masked_softmax(int dtype, void* P, const float* S, int rows, int n_keys, int H, int p0, int lo,
+                                        int window, float scale, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  LL_DISPATCH_DTYPE(dtype, ll_launch(latent_masked_softmax_kernel<T>, dim3(rows), dim3(256), 0, stream, (T*)P, S, rows,
+                                     n_keys, H, p0, lo, window, scale));
   return LL_LAUNCH_RESULT();
 }

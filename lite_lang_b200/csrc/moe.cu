@@ -28,12 +28,22 @@ moe_router_kernel(const T* __restrict__ x, long x_stride, const float* __restric
   if (t >= num_tokens) return;
   float* z = z_s[warp];
   const T* xr = x + (size_t)t * x_stride;
-  for (int e = 0; e < E; ++e) {
-    const float* wr = Wr + (size_t)e * hidden;
-    float acc = 0.f;
-    for (int i = lane; i < hidden; i += 32) acc = fmaf(wr[i], to_f32<T>(xr[i]), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) z[e] = acc;
+  // four experts at a time: one read of x for four independent sums (each in the fixed order of the lane's stride)
+  for (int e0 = 0; e0 < E; e0 += 4) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const float* wr = Wr + (size_t)e0 * hidden;
+    const int ne = min(4, E - e0);
+    for (int i = lane; i < hidden; i += 32) {
+      const float xv = to_f32<T>(xr[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (j < ne) acc[j] = fmaf(wr[(size_t)j * hidden + i], xv, acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = warp_sum(acc[j]);
+      if (lane == 0 && j < ne) z[e0 + j] = a;
+    }
   }
   __syncwarp();
   if (score_fn == 0) {
@@ -99,19 +109,38 @@ __device__ __forceinline__ float moe_activation(float z, int act) {
 }
 
 // h: T [tokens, shared_ff + E * ff] in place: h = act(h) * weight, weight 1 for the first shared_ff columns,
-// gates[t, (col - shared_ff) / ff] for the rest.
-template <typename T>
-__global__ void moe_act_kernel(T* __restrict__ h, const float* __restrict__ gates, long total, int width, int shared_ff,
-                               int ff, int E, int act) {
+// gates[t, (col - shared_ff) / ff] for the rest.  A thread takes VEC neighbouring columns of a row (one 16-byte
+// access where the row's width allows it).
+template <typename T, int VEC>
+__global__ void moe_act_kernel(T* __restrict__ h, const float* __restrict__ gates, int num_tokens, int width,
+                               int shared_ff, int ff, int E, int act) {
   LL_PDL_TRIGGER();
   LL_PDL_WAIT();
+  const int per_row = (width + VEC - 1) / VEC;
+  const long total = (long)num_tokens * per_row;
   const long step = (long)gridDim.x * blockDim.x;
   for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += step) {
-    const long t = idx / width;
-    const int c = (int)(idx - t * width);
-    const float w = c < shared_ff ? 1.f : gates[t * E + (c - shared_ff) / ff];
-    // an expert that was not chosen contributes an exact zero whatever its first product gave
-    h[idx] = from_f32<T>(w == 0.f ? 0.f : moe_activation(to_f32<T>(h[idx]), act) * w);
+    const int t = (int)(idx / per_row);
+    const int c0 = (int)(idx - (long)t * per_row) * VEC;
+    T* p = h + (size_t)t * width + c0;
+    T v[VEC];
+    if (VEC > 1) {
+      *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(p);
+    } else {
+      v[0] = p[0];
+    }
+#pragma unroll
+    for (int u = 0; u < VEC; ++u) {
+      const int c = c0 + u;
+      const float w = c < shared_ff ? 1.f : gates[(size_t)t * E + (c - shared_ff) / ff];
+      // an expert that was not chosen contributes an exact zero whatever its first product gave
+      v[u] = from_f32<T>(w == 0.f ? 0.f : moe_activation(to_f32<T>(v[u]), act) * w);
+    }
+    if (VEC > 1) {
+      *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(v);
+    } else {
+      p[0] = v[0];
+    }
   }
 }
 
@@ -131,11 +160,19 @@ extern "C" int ll_moe_act(int dtype, void* h, const float* gates, int num_tokens
   if (num_tokens <= 0) return 0;
   const int width = shared_ff + E * ff;
   if (width <= 0 || (E > 0 && ff <= 0)) return (int)cudaErrorInvalidValue;
-  const long total = (long)num_tokens * width;
   const long most = (long)(sms > 0 ? sms : 148) * 16;
-  const long want = (total + 255) / 256;
-  const int blocks = (int)(want < most ? want : most);
-  LL_DISPATCH_DTYPE(dtype, ll_launch(moe_act_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)h, gates, total, width,
-                                     shared_ff, ff, E, act));
+  LL_DISPATCH_DTYPE(dtype, {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    const bool wide = (width % VEC) == 0 && ((uintptr_t)h % 16) == 0;
+    const long total = (long)num_tokens * (wide ? width / VEC : width);
+    const long want = (total + 255) / 256;
+    const int blocks = (int)(want < most ? want : most);
+    if (wide)
+      ll_launch(moe_act_kernel<T, VEC>, dim3(blocks), dim3(256), 0, stream, (T*)h, gates, num_tokens, width, shared_ff,
+                ff, E, act);
+    else
+      ll_launch(moe_act_kernel<T, 1>, dim3(blocks), dim3(256), 0, stream, (T*)h, gates, num_tokens, width, shared_ff,
+                ff, E, act);
+  });
   return LL_LAUNCH_RESULT();
 }

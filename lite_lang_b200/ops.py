@@ -1060,40 +1060,63 @@ def delta_out(out: torch.Tensor, o: torch.Tensor, weight: torch.Tensor, gate: to
 # --------------------------------------------------------------------------
 def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, norm_w: torch.Tensor, eps: float, freq: torch.Tensor,
                    rot_dims: int, positions: torch.Tensor, slot_map: Optional[torch.Tensor], cache: torch.Tensor,
-                   q_rot: torch.Tensor, H: int, d: int, r: int, R: int, status: Optional[torch.Tensor]) -> None:
+                   q_full: torch.Tensor, H: int, d: int, r: int, R: int, status: Optional[torch.Tensor]) -> None:
     """Per token: the latent's RMS norm and the rotated key part into the cache row, and every head's rotated
-    query part into ``q_rot`` (float32 [tokens, H, r])."""
-    _need_cuda(proj, norm_w, freq, positions, slot_map, cache, q_rot)
+    query part into ``q_full`` [tokens, H, R + r] behind the R latent-space numbers (which a product fills)."""
+    _need_cuda(proj, norm_w, freq, positions, slot_map, cache, q_full)
     _f32(norm_w, "norm_w")
     _f32(freq, "freq")
-    _f32(q_rot, "q_rot")
     _i32(positions, "positions")
     _i32(slot_map, "slot_map")
     _need(proj.stride(1) == 1 and cache.is_contiguous() and cache.dtype == proj.dtype and cache.shape[-1] == R + r
           and cache.shape[1] == 1, "latent_prepare: the cache plane is [pages, 1, page, latent + rotated]")
+    _need(q_full.is_contiguous() and q_full.dtype == proj.dtype and tuple(q_full.shape[1:]) == (H, R + r),
+          "latent_prepare: q_full is [tokens, H, latent + rotated] of the projections' dtype")
     load_library("latent_attn").call(
         "ll_latent_prepare", c_int(_dtype_code(proj)), _ptr(proj), c_long(proj.stride(0)), c_int(q_off), c_int(kv_off),
         _ptr(norm_w), c_float(eps), _ptr(freq), c_int(rot_dims), _ptr(positions), _ptr(slot_map), _ptr(cache),
-        c_long(cache.shape[0] * cache.shape[2]), _ptr(q_rot), c_int(proj.shape[0]), c_int(H), c_int(d), c_int(r),
+        c_long(cache.shape[0] * cache.shape[2]), _ptr(q_full), c_int(proj.shape[0]), c_int(H), c_int(d), c_int(r),
         c_int(R), _ptr(status), _stream())
 
 
-def latent_attention(out: torch.Tensor, qa: torch.Tensor, q_rot: torch.Tensor, cache: torch.Tensor,
-                     block_table: torch.Tensor, step, H: int, R: int, r: int, page_size: int,
-                     window: Optional[int], scale: float) -> None:
-    """Attention in the latent space.  ``qa`` float32 [H, tokens, R] (any strides with unit inner stride),
-    ``out`` [H, tokens, R] of the cache's dtype (likewise): sum_j p_j c_j per head."""
-    _need_cuda(out, qa, q_rot, cache, block_table)
-    _need(qa.dtype == torch.float32 and qa.stride(2) == 1 and out.stride(2) == 1 and out.dtype == cache.dtype,
-          "latent_attention: layouts")
+def latent_attention(out: torch.Tensor, q_full: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, step,
+                     first: int, count: int, H: int, R: int, r: int, page_size: int, window: Optional[int],
+                     scale: float) -> None:
+    """Attention in the latent space for tokens ``first .. first + count - 1`` of the step.  ``q_full``
+    [tokens, H, R + r] and ``out`` [tokens, H, R] (sum_j p_j c_j per head) have the cache's dtype."""
+    _need_cuda(out, q_full, cache, block_table)
+    _need(q_full.is_contiguous() and out.is_contiguous() and q_full.dtype == cache.dtype == out.dtype
+          and tuple(q_full.shape[1:]) == (H, R + r) and tuple(out.shape[1:]) == (H, R), "latent_attention: layouts")
     _need(R <= 512, f"latent_attention: a latent of {R} numbers is wider than the kernel takes (512)")
-    n = qa.shape[1]
+    _need(0 <= first and first + count <= q_full.shape[0], "latent_attention: token range")
     load_library("latent_attn").call(
-        "ll_latent_attention", c_int(_dtype_code(out)), _ptr(out), c_long(out.stride(0)), c_long(out.stride(1)),
-        _ptr(qa), c_long(qa.stride(0)), c_long(qa.stride(1)), _ptr(q_rot), _ptr(cache), _ptr(block_table),
-        c_int(block_table.stride(0)), _ptr(step.token_req), _ptr(step.req_slot), _ptr(step.positions), c_int(n),
-        c_int(H), c_int(R), c_int(r), c_int(page_size), c_int(cache.shape[0]), c_int(window or 0), c_float(scale),
-        _ptr(step.status), _stream())
+        "ll_latent_attention", c_int(_dtype_code(out)), _ptr(out), _ptr(q_full), _ptr(cache), _ptr(block_table),
+        c_int(block_table.stride(0)), _ptr(step.token_req), _ptr(step.req_slot), _ptr(step.positions), c_int(first),
+        c_int(count), c_int(H), c_int(R), c_int(r), c_int(page_size), c_int(cache.shape[0]), c_int(window or 0),
+        c_float(scale), _ptr(step.status), _stream())
+
+
+def latent_gather(dst: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, slot: int, lo: int, page_size: int,
+                  status: Optional[torch.Tensor]) -> None:
+    """dst [n, width] = the cached rows of positions lo .. lo + n - 1 of the request in ``slot``."""
+    _need_cuda(dst, cache, block_table)
+    _need(dst.is_contiguous() and dst.dtype == cache.dtype and dst.shape[1] == cache.shape[-1], "latent_gather: dst")
+    row = block_table[slot]
+    load_library("latent_attn").call(
+        "ll_latent_gather", c_int(_dtype_code(dst)), _ptr(dst), _ptr(cache), _ptr(row), c_int(lo), c_int(dst.shape[0]),
+        c_int(dst.shape[1]), c_int(page_size), c_int(cache.shape[0]), _ptr(status), _stream())
+
+
+def latent_masked_softmax(P: torch.Tensor, S: torch.Tensor, H: int, p0: int, lo: int, window: Optional[int],
+                          scale: float) -> None:
+    """P = softmax(scale * S) over the keys each row may see, zero elsewhere.  Row i is query position
+    p0 + i // H; column j is key position lo + j; a query at p sees max(lo, p - window + 1) .. p."""
+    _need_cuda(P, S)
+    _f32(S, "S")
+    _need(P.is_contiguous() and tuple(P.shape) == tuple(S.shape), "latent_masked_softmax: shapes")
+    load_library("latent_attn").call(
+        "ll_latent_masked_softmax", c_int(_dtype_code(P)), _ptr(P), _ptr(S), c_int(S.shape[0]), c_int(S.shape[1]),
+        c_int(H), c_int(p0), c_int(lo), c_int(window or 0), c_float(scale), _stream())
 
 
 def batched_heads(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
@@ -1107,6 +1130,15 @@ def batched_heads(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] 
     if out_dtype is not None and out_dtype != a.dtype:
         return torch.bmm(a, b, out_dtype=out_dtype)
     return torch.bmm(a, b)
+
+
+def product(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Library product a [n, k] times b [k, m] (b not transposed, any row stride): true float32 for float32
+    operands, float32 accumulation for bfloat16 ones."""
+    _need_cuda(a, b, out)
+    if a.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
+        raise RuntimeError("TF32 is on; call ops.configure_matmul_precision() before a float32 product")
+    return torch.mm(a, b, out=out) if out is not None else torch.mm(a, b)
 
 
 # --------------------------------------------------------------------------

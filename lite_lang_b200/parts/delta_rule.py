@@ -121,7 +121,7 @@ class GatedDeltaRule(Mixer):
             rows.append(w.to(dtype))
             pad = _pad8(w.shape[0]) - w.shape[0]
             if pad:
-                rows.append(torch.zeros((pad, h), dtype=dtype))
+                rows.append(torch.zeros((pad, h), dtype=dtype, device=w.device))
             at += _pad8(w.shape[0])
         self.w_in = torch.cat(rows, dim=0).to(device).contiguous()
         self.conv_q, self.conv_k, self.conv_v = f32("q.conv"), f32("k.conv"), f32("v.conv")

@@ -67,7 +67,7 @@ class LatentAttention(Mixer):
         self.kv_off = (q.shape[0] + 7) // 8 * 8
         rows = [q]
         if self.kv_off != q.shape[0]:
-            rows.append(torch.zeros((self.kv_off - q.shape[0], self.hidden_size), dtype=dtype))
+            rows.append(torch.zeros((self.kv_off - q.shape[0], self.hidden_size), dtype=dtype, device=q.device))
         rows.append(fetch("dkv").to(dtype))
         self.w_in = torch.cat(rows, dim=0).to(device).contiguous()
         self.norm_w = fetch("dkv.norm").to(torch.float32).to(device).contiguous()
@@ -91,20 +91,60 @@ class LatentAttention(Mixer):
             libs.extend(["gemm_smallm", "gemm_stream", "gemm_tc"])
         return libs
 
+    # Prompt portions of at least this many tokens go through library products (scores and weighted sums of a
+    # block of queries against the run of cached rows they see); shorter ones and single tokens go to the kernel
+    # that walks each query's keys itself.
+    PRODUCT_MIN_TOKENS = 32
+    QUERY_BLOCK = 256
+
     def forward(self, x, step, cache):
         n, dev, H, d, r, R = x.shape[0], x.device, self.H, self.d, self.r, self.R
         proj = ops.linear(x, self.w_in)
-        q_rot = torch.empty((n, H, r), dtype=torch.float32, device=dev)
+        q_full = torch.empty((n, H, R + r), dtype=x.dtype, device=dev)
         ops.latent_prepare(proj, 0, self.kv_off, self.norm_w, self.eps, self.freq, self.rot_dims, step.positions,
-                           cache.slot_map if cache.writable else None, cache.k, q_rot, H, d, r, R, step.status)
+                           cache.slot_map if cache.writable else None, cache.k, q_full, H, d, r, R, step.status)
+        # queries into the latent space: a_h = Uk_h^T q_h, written in front of the rotated parts
         q_plain = proj[:, :H * (d + r)].view(n, H, d + r)[:, :, :d].permute(1, 0, 2)          # [H, n, d]
-        qa = ops.batched_heads(q_plain, self.w_uk, out_dtype=torch.float32)                     # [H, n, R]
-        lat = torch.empty((H, n, R), dtype=x.dtype, device=dev)
-        ops.latent_attention(lat, qa, q_rot, cache.k, cache.block_table, step, H, R, r, cache.page_size,
-                             self.window, self.scale)
+        ops.batched_heads(q_plain, self.w_uk, out=q_full[:, :, :R].permute(1, 0, 2))            # [H, n, R]
+        lat = torch.empty((n, H, R), dtype=x.dtype, device=dev)
+        self.attend(lat, q_full, step, cache)
         heads = torch.empty((n, H * self.dv), dtype=x.dtype, device=dev)
-        ops.batched_heads(lat, self.w_uv_t, out=heads.view(n, H, self.dv).permute(1, 0, 2))
+        ops.batched_heads(lat.permute(1, 0, 2), self.w_uv_t, out=heads.view(n, H, self.dv).permute(1, 0, 2))
         return ops.linear(heads, self.w_o)
+
+    def attend(self, lat, q_full, step, cache) -> None:
+        n, H, R, r = q_full.shape[0], self.H, self.R, self.r
+        args = (H, R, r, cache.page_size, self.window, self.scale)
+        entries = None if getattr(step, "captured", False) else getattr(step, "entries", None)
+        if entries is None or all(len(e.tokens) < self.PRODUCT_MIN_TOKENS for e in entries):
+            ops.latent_attention(lat, q_full, cache.k, cache.block_table, step, 0, n, *args)
+            return
+        t, run0 = 0, 0          # run0: first token of the current run of entries that go to the kernel
+        for e, ctx in zip(entries, step.entry_ctx):
+            q = len(e.tokens)
+            if q >= self.PRODUCT_MIN_TOKENS:
+                if t > run0:
+                    ops.latent_attention(lat, q_full, cache.k, cache.block_table, step, run0, t - run0, *args)
+                self._attend_by_products(lat, q_full, cache, step, e.slot, t, q, ctx)
+                run0 = t + q
+            t += q
+        if n > run0:     # (padding entries of a captured step never come here: such a step has no host entries)
+            ops.latent_attention(lat, q_full, cache.k, cache.block_table, step, run0, n - run0, *args)
+
+    def _attend_by_products(self, lat, q_full, cache, step, slot, t0, count, ctx) -> None:
+        """Tokens t0 .. t0 + count - 1 of the step: one request's positions ctx .. ctx + count - 1."""
+        H, R, KD = self.H, self.R, self.R + self.r
+        for b0 in range(0, count, self.QUERY_BLOCK):
+            nb = min(self.QUERY_BLOCK, count - b0)
+            p0 = ctx + b0
+            lo = max(0, p0 - self.window + 1) if self.window else 0
+            keys = torch.empty((p0 + nb - lo, KD), dtype=lat.dtype, device=lat.device)
+            ops.latent_gather(keys, cache.k, cache.block_table, slot, lo, cache.page_size, step.status)
+            qb = q_full[t0 + b0:t0 + b0 + nb].view(nb * H, KD)
+            scores = ops.linear(qb, keys, out_dtype=torch.float32)                       # [nb * H, keys]
+            weights = torch.empty(scores.shape, dtype=lat.dtype, device=lat.device)
+            ops.latent_masked_softmax(weights, scores, H, p0, lo, self.window, self.scale)
+            ops.product(weights, keys[:, :R], out=lat[t0 + b0:t0 + b0 + nb].view(nb * H, R))
 
 
 register_part("mixer", "latent_attention", LatentAttention)
