@@ -131,25 +131,29 @@ __global__ void delta_conv_update_kernel(const T* __restrict__ proj, long proj_s
 }
 
 // The scan.  A block of 128 threads owns 16 value columns of one (entry, head); 8 lanes share a column, lane l
-// holding key channels l, l + 8, ... in NR registers.  q, k (and a per-channel decay) of a token go through
-// shared memory, double-buffered: the next token's numbers are asked for (into registers) before the current
-// token is worked on and put into the other buffer after it, so that their way from memory lies under the
-// arithmetic.  Sums run in two interleaved chains (even and odd registers) in a fixed order.
+// holding key channels l, l + 8, ... in NR registers.  The tokens' q, k, decay, v and beta come through shared
+// memory in chunks of DR_CH tokens, copied asynchronously (cp.async) a chunk ahead, so that the scan itself waits
+// for memory once a chunk and meets no barrier between the tokens of a chunk.  Sums run in two interleaved chains
+// (even and odd registers) and then over the 8 lanes, in a fixed order.
 #define DR_COLS 16
 #define DR_LANES 8
-#define DR_NF 2      // shared-memory numbers a thread fetches per token and array: covers dk <= 256
+#define DR_CH 8
+__device__ __forceinline__ void dr_copy4(float* dst_smem, const float* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst_smem);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
 template <int NR>
 __global__ void __launch_bounds__(DR_COLS * DR_LANES)
 delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vc,
                         const float* __restrict__ beta, const float* __restrict__ g, float* __restrict__ state,
                         long state_stride, const int* __restrict__ cu_q, const int* __restrict__ req_slot,
                         float* __restrict__ o, DeltaShape s) {
-  extern __shared__ float sm[];   // [2][3][dk]: q, k, decay of a token, double-buffered
+  extern __shared__ float sm[];   // two buffers of [q | k | decay][DR_CH][dk], v [DR_CH][DR_COLS], beta, head decay [DR_CH]
   LL_PDL_TRIGGER();
   LL_PDL_WAIT();
   const int e = blockIdx.x, h = blockIdx.y;
-  const int tid = threadIdx.x, l = tid % DR_LANES;
-  const int col = blockIdx.z * DR_COLS + tid / DR_LANES;
+  const int tid = threadIdx.x, l = tid % DR_LANES, cl = tid / DR_LANES;
+  const int col0 = blockIdx.z * DR_COLS, col = col0 + cl;
   const bool live_col = col < s.dv;
   const int first = cu_q[e], last = cu_q[e + 1];
   const int slot = req_slot[e];
@@ -162,6 +166,7 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
   const int hk = h / (s.H / s.Hk);
   const int ng = s.per_channel ? s.H * dk : s.H;
   const bool pc = s.per_channel != 0;
+  const int buf_floats = DR_CH * (3 * dk + DR_COLS + 2);
   float* S_ptr = state + (size_t)slot * state_stride + (size_t)h * dk * s.dv;
   float S[NR];
 #pragma unroll
@@ -169,82 +174,80 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
     const int c = l + DR_LANES * i;
     S[i] = (live_col && c < dk) ? S_ptr[(size_t)c * s.dv + col] : 0.f;
   }
-  // what this thread brings of a token: up to DR_NF numbers of q, k and the decay, and its own v, beta, decay
-  float fq[DR_NF], fk[DR_NF], fg[DR_NF], fv = 0.f, fb = 0.f, fgh = 1.f;
-  auto fetch = [&](int t) {
-#pragma unroll
-    for (int u = 0; u < DR_NF; ++u) {
-      const int i = tid + u * DR_COLS * DR_LANES;
-      if (i < dk) {
-        fq[u] = qn[(size_t)t * Cq + (size_t)hk * dk + i];
-        fk[u] = kn[(size_t)t * Cq + (size_t)hk * dk + i];
-        if (pc) fg[u] = g[(size_t)t * ng + (size_t)h * dk + i];
-      }
+  auto load_chunk = [&](int t0, int buf) {
+    float* b = sm + (size_t)buf * buf_floats;
+    const int nt = min(DR_CH, last - t0);
+    for (int idx = tid; idx < nt * dk; idx += DR_COLS * DR_LANES) {
+      const int i = idx / dk, c = idx - i * dk;
+      dr_copy4(b + idx, qn + (size_t)(t0 + i) * Cq + (size_t)hk * dk + c);
+      dr_copy4(b + DR_CH * dk + idx, kn + (size_t)(t0 + i) * Cq + (size_t)hk * dk + c);
+      if (pc) dr_copy4(b + 2 * DR_CH * dk + idx, g + (size_t)(t0 + i) * ng + (size_t)h * dk + c);
     }
-    fv = live_col ? vc[(size_t)t * Cv + (size_t)h * s.dv + col] : 0.f;
-    fb = beta[(size_t)t * s.H + h];
-    if (!pc) fgh = g[(size_t)t * ng + h];
+    float* bv = b + 3 * DR_CH * dk;
+    for (int idx = tid; idx < nt * DR_COLS; idx += DR_COLS * DR_LANES) {
+      const int i = idx / DR_COLS, cc = idx % DR_COLS;
+      if (col0 + cc < s.dv) dr_copy4(bv + idx, vc + (size_t)(t0 + i) * Cv + (size_t)h * s.dv + col0 + cc);
+      else bv[idx] = 0.f;
+    }
+    if (tid < nt) {
+      dr_copy4(bv + DR_CH * DR_COLS + tid, beta + (size_t)(t0 + tid) * s.H + h);
+      if (!pc) dr_copy4(bv + DR_CH * DR_COLS + DR_CH + tid, g + (size_t)(t0 + tid) * ng + h);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  auto put = [&](int buf) {
-    float* b = sm + (size_t)buf * 3 * dk;
-#pragma unroll
-    for (int u = 0; u < DR_NF; ++u) {
-      const int i = tid + u * DR_COLS * DR_LANES;
-      if (i < dk) {
-        b[i] = fq[u];
-        b[dk + i] = fk[u];
-        if (pc) b[2 * dk + i] = fg[u];
-      }
-    }
-  };
-  float v = 0.f, b = 0.f, gh = 1.f;
-  if (first < last) {
-    fetch(first);
-    put(0);
-    v = fv, b = fb, gh = fgh;
-  }
-  __syncthreads();
-  for (int t = first; t < last; ++t) {
-    const int buf = (t - first) & 1;
-    if (t + 1 < last) fetch(t + 1);
-    const float* sq = sm + (size_t)buf * 3 * dk;
-    const float* sk = sq + dk;
-    const float* sg = sk + dk;
-    float kr[NR];
-    float d0 = 0.f, d1 = 0.f;
-#pragma unroll
-    for (int i = 0; i < NR; ++i) {
-      const int c = l + DR_LANES * i;
-      kr[i] = c < dk ? sk[c] : 0.f;
-      const float dec = pc ? (c < dk ? sg[c] : 1.f) : gh;
-      S[i] *= dec;
-      if (i & 1) d1 = fmaf(S[i], kr[i], d1);
-      else d0 = fmaf(S[i], kr[i], d0);
-    }
-    float dot = d0 + d1;
-    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-    dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-    const float u = b * (v - dot);
-    float o0 = 0.f, o1 = 0.f;
-#pragma unroll
-    for (int i = 0; i < NR; ++i) {
-      const int c = l + DR_LANES * i;
-      const float qv = c < dk ? sq[c] : 0.f;
-      S[i] = fmaf(kr[i], u, S[i]);
-      if (i & 1) o1 = fmaf(S[i], qv, o1);
-      else o0 = fmaf(S[i], qv, o0);
-    }
-    float oq = o0 + o1;
-    oq += __shfl_xor_sync(0xffffffffu, oq, 1);
-    oq += __shfl_xor_sync(0xffffffffu, oq, 2);
-    oq += __shfl_xor_sync(0xffffffffu, oq, 4);
-    if (live_col && l == 0) o[(size_t)t * Cv + (size_t)h * s.dv + col] = oq;
-    if (t + 1 < last) {
-      put(buf ^ 1);
-      v = fv, b = fb, gh = fgh;
+  if (first < last) load_chunk(first, 0);
+  for (int t0 = first; t0 < last; t0 += DR_CH) {
+    const int buf = ((t0 - first) / DR_CH) & 1;
+    const bool more = t0 + DR_CH < last;
+    if (more) {
+      load_chunk(t0 + DR_CH, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
+    const float* b = sm + (size_t)buf * buf_floats;
+    const float* bv = b + 3 * DR_CH * dk;
+    const int nt = min(DR_CH, last - t0);
+    for (int i = 0; i < nt; ++i) {
+      const float* sq = b + i * dk;
+      const float* sk = b + DR_CH * dk + i * dk;
+      const float* sg = b + 2 * DR_CH * dk + i * dk;
+      const float v = bv[i * DR_COLS + cl];
+      const float bt = bv[DR_CH * DR_COLS + i];
+      const float gh = pc ? 1.f : bv[DR_CH * DR_COLS + DR_CH + i];
+      float kr[NR];
+      float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < NR; ++j) {
+        const int c = l + DR_LANES * j;
+        kr[j] = c < dk ? sk[c] : 0.f;
+        const float dec = pc ? (c < dk ? sg[c] : 1.f) : gh;
+        S[j] *= dec;
+        if (j & 1) d1 = fmaf(S[j], kr[j], d1);
+        else d0 = fmaf(S[j], kr[j], d0);
+      }
+      float dot = d0 + d1;
+      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+      const float u = bt * (v - dot);
+      float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < NR; ++j) {
+        const int c = l + DR_LANES * j;
+        const float qv = c < dk ? sq[c] : 0.f;
+        S[j] = fmaf(kr[j], u, S[j]);
+        if (j & 1) o1 = fmaf(S[j], qv, o1);
+        else o0 = fmaf(S[j], qv, o0);
+      }
+      float oq = o0 + o1;
+      oq += __shfl_xor_sync(0xffffffffu, oq, 1);
+      oq += __shfl_xor_sync(0xffffffffu, oq, 2);
+      oq += __shfl_xor_sync(0xffffffffu, oq, 4);
+      if (live_col && l == 0) o[(size_t)(t0 + i) * Cv + (size_t)h * s.dv + col] = oq;
+    }
+    __syncthreads();   // everyone is done with this buffer before the chunk after the next is copied into it
   }
 #pragma unroll
   for (int i = 0; i < NR; ++i) {
@@ -314,7 +317,7 @@ extern "C" int ll_delta_recurrence(const float* qn, const float* kn, const float
   if (H <= 0 || Hk <= 0 || H % Hk || dk <= 0 || dk > 256 || dv <= 0) return (int)cudaErrorInvalidValue;
   DeltaShape s{H, Hk, dk, dv, 0, per_channel};
   dim3 grid(num_entries, H, (dv + DR_COLS - 1) / DR_COLS), block(DR_COLS * DR_LANES);
-  const size_t smem = sizeof(float) * 6 * (size_t)dk;
+  const size_t smem = sizeof(float) * 2 * DR_CH * (3 * (size_t)dk + DR_COLS + 2);
   if (dk <= 32)
     ll_launch(delta_recurrence_kernel<4>, grid, block, smem, stream, qn, kn, vc, beta, g, state, state_stride, cu_q,
               req_slot, o, s);

@@ -271,14 +271,21 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
   }
 }
 
-// Rows lo .. lo + n - 1 of a request's cached rows, copied out of their pages into dst [n, KD].
+// Rows first .. last of a request's cached rows, copied out of their pages into dst [n, KD], row j being
+// position lo + j; rows of positions outside first .. last are zeros (the run is padded to a width that
+// library products like).
 template <typename T>
 __global__ void latent_gather_kernel(T* __restrict__ dst, const T* __restrict__ cache, const int* __restrict__ bt,
-                                     int lo, int n, int KD, int page_size, int num_pages, int* status) {
+                                     int lo, int first, int last, int n, int KD, int page_size, int num_pages,
+                                     int* status) {
   LL_PDL_TRIGGER();
   LL_PDL_WAIT();
   for (int j = blockIdx.x; j < n; j += gridDim.x) {
     const int pos = lo + j;
+    if (pos < first || pos > last) {
+      for (int c = threadIdx.x; c < KD; c += blockDim.x) dst[(size_t)j * KD + c] = from_f32<T>(0.f);
+      continue;
+    }
     const int page = bt[pos / page_size];
     const bool ok = page >= 0 && page < num_pages;
     if (!ok && threadIdx.x == 0) set_status(status, LL_ERR_PAGE_RANGE);
@@ -344,11 +351,11 @@ extern "C" int ll_latent_attention(int dtype, void* out, const void* q, const vo
   return LL_LAUNCH_RESULT();
 }
 
-extern "C" int ll_latent_gather(int dtype, void* dst, const void* cache, const int* bt_row, int lo, int n, int KD,
-                                int page_size, int num_pages, int* status, cudaStream_t stream) {
+extern "C" int ll_latent_gather(int dtype, void* dst, const void* cache, const int* bt_row, int lo, int first, int last,
+                                int n, int KD, int page_size, int num_pages, int* status, cudaStream_t stream) {
   if (n <= 0) return 0;
   LL_DISPATCH_DTYPE(dtype, ll_launch(latent_gather_kernel<T>, dim3(n < 1024 ? n : 1024), dim3(128), 0, stream, (T*)dst,
-                                     (const T*)cache, bt_row, lo, n, KD, page_size, num_pages, status));
+                                     (const T*)cache, bt_row, lo, first, last, n, KD, page_size, num_pages, status));
   return LL_LAUNCH_RESULT();
 }
 

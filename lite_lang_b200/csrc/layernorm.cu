@@ -1,6 +1,9 @@
 // Layer norm with a weight and no bias over a float32 residual stream, fused with the residual sum.
 //
-//   r = residual + (d1 + d2)                  (float32; d1, d2 optional, stored as T)
+//   r = residual + (d1 + d2)                  (float32; d1, d2 optional, stored as T; d2 may instead come as
+//                                              float32 partial sums of a product split over its inner
+//                                              dimension, which are added up and rounded to T first, as the
+//                                              unsplit product's result would have been)
 //   y = (r - mean(r)) / sqrt(var(r) + eps) * w       (var = mean of the squared deviations)
 //
 // The residual stream stays float32 whatever the storage type T of the activations is: r is
@@ -12,7 +15,8 @@
 
 template <typename T>
 __global__ void add_layernorm_kernel(T* __restrict__ out, float* __restrict__ residual, const T* __restrict__ d1,
-                                     const T* __restrict__ d2, const float* __restrict__ w, float eps, int hidden,
+                                     const T* __restrict__ d2, const float* __restrict__ partial, int parts,
+                                     long part_stride, const float* __restrict__ w, float eps, int hidden,
                                      const int* __restrict__ rows, int write_residual) {
   extern __shared__ float row[];
   __shared__ float scratch[32];
@@ -23,12 +27,18 @@ __global__ void add_layernorm_kernel(T* __restrict__ out, float* __restrict__ re
   float* res = residual + (size_t)r * hidden;
   const T* a = d1 ? d1 + (size_t)r * hidden : nullptr;
   const T* b = d2 ? d2 + (size_t)r * hidden : nullptr;
+  const float* par = partial ? partial + (size_t)r * hidden : nullptr;
   float s = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float v = res[i];
-    if (a || b) {
+    if (a || b || par) {
       float d = a ? to_f32<T>(a[i]) : 0.f;
       if (b) d += to_f32<T>(b[i]);
+      if (par) {
+        float ps = 0.f;
+        for (int q = 0; q < parts; ++q) ps += par[(size_t)q * part_stride + i];
+        d += round_to<T>(ps);
+      }
       v += d;
       if (write_residual) res[i] = v;
     }
@@ -47,9 +57,9 @@ __global__ void add_layernorm_kernel(T* __restrict__ out, float* __restrict__ re
 }
 
 // out: [n_out, hidden] of T; residual: float32 [tokens, hidden]; d1, d2: T [tokens, hidden] or null.
-extern "C" int ll_add_layernorm(int dtype, void* out, float* residual, const void* d1, const void* d2, const float* w,
-                                float eps, int n_out, int hidden, const int* rows, int write_residual,
-                                cudaStream_t stream) {
+extern "C" int ll_add_layernorm(int dtype, void* out, float* residual, const void* d1, const void* d2,
+                                const float* partial, int parts, long part_stride, const float* w, float eps, int n_out,
+                                int hidden, const int* rows, int write_residual, cudaStream_t stream) {
   if (n_out <= 0) return 0;
   if (hidden <= 0) return (int)cudaErrorInvalidValue;
   const size_t smem = sizeof(float) * (size_t)hidden;
@@ -58,7 +68,7 @@ extern "C" int ll_add_layernorm(int dtype, void* out, float* residual, const voi
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(add_layernorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ll_launch(add_layernorm_kernel<T>, dim3(n_out), dim3(threads), smem, stream, (T*)out, residual, (const T*)d1,
-              (const T*)d2, w, eps, hidden, rows, write_residual);
+              (const T*)d2, partial, parts, part_stride, w, eps, hidden, rows, write_residual);
   });
   return LL_LAUNCH_RESULT();
 }

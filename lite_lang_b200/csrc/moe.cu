@@ -14,38 +14,40 @@
 #define MOE_MAX_E 256
 
 // Wr: float32 [E, hidden]; x: T [tokens, hidden]; gates: float32 [tokens, E]; top_idx int32 / top_w float32
-// [tokens, top].  score_fn: 0 softmax, 1 sigmoid.  One warp per token.
+// [tokens, top].  score_fn: 0 softmax, 1 sigmoid.  One block per token: its four warps share out the experts
+// (each sum runs over a lane's stride of the row, then over the lanes: an order that depends on the sizes
+// only), then the first warp scores and picks.
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_router_kernel(const T* __restrict__ x, long x_stride, const float* __restrict__ Wr, float* __restrict__ gates,
                   int* __restrict__ top_idx, float* __restrict__ top_w, int num_tokens, int hidden, int E, int top,
                   int score_fn, int renormalize) {
-  __shared__ float z_s[4][MOE_MAX_E];
+  __shared__ float z[MOE_MAX_E];
   LL_PDL_TRIGGER();
   LL_PDL_WAIT();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 4 + warp;
-  if (t >= num_tokens) return;
-  float* z = z_s[warp];
+  const int t = blockIdx.x;
   const T* xr = x + (size_t)t * x_stride;
-  // four experts at a time: one read of x for four independent sums (each in the fixed order of the lane's stride)
-  for (int e0 = 0; e0 < E; e0 += 4) {
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    const float* wr = Wr + (size_t)e0 * hidden;
-    const int ne = min(4, E - e0);
+  for (int e0 = warp * 2; e0 < E; e0 += 8) {      // two experts a pass: one read of x for two sums
+    const bool two = e0 + 1 < E;
+    const float* w0 = Wr + (size_t)e0 * hidden;
+    const float* w1 = Wr + (size_t)(two ? e0 + 1 : e0) * hidden;
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll 8
     for (int i = lane; i < hidden; i += 32) {
       const float xv = to_f32<T>(xr[i]);
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        if (j < ne) acc[j] = fmaf(wr[(size_t)j * hidden + i], xv, acc[j]);
+      a0 = fmaf(w0[i], xv, a0);
+      a1 = fmaf(w1[i], xv, a1);
     }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float a = warp_sum(acc[j]);
-      if (lane == 0 && j < ne) z[e0 + j] = a;
+    a0 = warp_sum(a0);
+    a1 = warp_sum(a1);
+    if (lane == 0) {
+      z[e0] = a0;
+      if (two) z[e0 + 1] = a1;
     }
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   if (score_fn == 0) {
     float m = -INFINITY;
     for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
@@ -125,6 +127,12 @@ __global__ void moe_act_kernel(T* __restrict__ h, const float* __restrict__ gate
     T* p = h + (size_t)t * width + c0;
     T v[VEC];
     if (VEC > 1) {
+      // the piece lies inside one expert (the launcher checked the widths): if that expert was not chosen for
+      // the token, zeros are written and nothing is read
+      if (c0 >= shared_ff && gates[(size_t)t * E + (c0 - shared_ff) / ff] == 0.f) {
+        *reinterpret_cast<uint4*>(p) = make_uint4(0, 0, 0, 0);
+        continue;
+      }
       *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(p);
     } else {
       v[0] = p[0];
@@ -149,7 +157,7 @@ extern "C" int ll_moe_router(int dtype, const void* x, long x_stride, const floa
                              cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (E <= 0 || E > MOE_MAX_E || top <= 0 || top > E || hidden <= 0) return (int)cudaErrorInvalidValue;
-  LL_DISPATCH_DTYPE(dtype, ll_launch(moe_router_kernel<T>, dim3((num_tokens + 3) / 4), dim3(128), 0, stream,
+  LL_DISPATCH_DTYPE(dtype, ll_launch(moe_router_kernel<T>, dim3(num_tokens), dim3(128), 0, stream,
                                      (const T*)x, x_stride, Wr, gates, top_idx, top_w, num_tokens, hidden, E, top,
                                      score_fn, renormalize));
   return LL_LAUNCH_RESULT();
@@ -163,7 +171,7 @@ extern "C" int ll_moe_act(int dtype, void* h, const float* gates, int num_tokens
   const long most = (long)(sms > 0 ? sms : 148) * 16;
   LL_DISPATCH_DTYPE(dtype, {
     constexpr int VEC = 16 / (int)sizeof(T);
-    const bool wide = (width % VEC) == 0 && ((uintptr_t)h % 16) == 0;
+    const bool wide = (width % VEC) == 0 && (shared_ff % VEC) == 0 && (ff % VEC) == 0 && ((uintptr_t)h % 16) == 0;
     const long total = (long)num_tokens * (wide ? width / VEC : width);
     const long want = (total + 255) / 256;
     const int blocks = (int)(want < most ? want : most);

@@ -983,9 +983,11 @@ def embed_scaled_f32(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, 
 
 
 def add_layernorm(out: torch.Tensor, residual: torch.Tensor, d1: Optional[torch.Tensor], d2: Optional[torch.Tensor],
-                  weight: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None) -> None:
+                  weight: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None,
+                  partial: Optional[torch.Tensor] = None) -> None:
     """residual (float32) += d1 + d2 (written back unless ``rows`` selects rows); out = layer norm of it
-    times ``weight``, in ``out``'s dtype."""
+    times ``weight``, in ``out``'s dtype.  ``partial``: a further addend as float32 partial sums
+    [parts, tokens, hidden] of a product that was split over its inner dimension."""
     _need_cuda(out, residual, d1, d2, weight, rows)
     _f32(weight, "norm weight")
     _f32(residual, "residual")
@@ -998,9 +1000,15 @@ def add_layernorm(out: torch.Tensor, residual: torch.Tensor, d1: Optional[torch.
     n_out = rows.numel() if rows is not None else residual.shape[0]
     _need(out.is_contiguous() and out.shape[0] >= n_out and out.shape[1] == hidden and weight.numel() == hidden,
           "add_layernorm: out shape")
+    parts, part_stride = 0, 0
+    if partial is not None:
+        _need(partial.dtype == torch.float32 and partial.is_contiguous() and partial.dim() == 3
+              and tuple(partial.shape[1:]) == tuple(residual.shape), "add_layernorm: partial sums are float32 "
+              "[parts, tokens, hidden]")
+        parts, part_stride = partial.shape[0], partial.shape[1] * hidden
     core().call("ll_add_layernorm", c_int(_dtype_code(out)), _ptr(out), _ptr(residual), _ptr(d1), _ptr(d2),
-                _ptr(weight), c_float(eps), c_int(n_out), c_int(hidden), _ptr(rows), c_int(1 if rows is None else 0),
-                _stream())
+                _ptr(partial), c_int(parts), c_long(part_stride), _ptr(weight), c_float(eps), c_int(n_out),
+                c_int(hidden), _ptr(rows), c_int(1 if rows is None else 0), _stream())
 
 
 # --------------------------------------------------------------------------
@@ -1097,14 +1105,18 @@ def latent_attention(out: torch.Tensor, q_full: torch.Tensor, cache: torch.Tenso
 
 
 def latent_gather(dst: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, slot: int, lo: int, page_size: int,
-                  status: Optional[torch.Tensor]) -> None:
-    """dst [n, width] = the cached rows of positions lo .. lo + n - 1 of the request in ``slot``."""
+                  status: Optional[torch.Tensor], first: Optional[int] = None, last: Optional[int] = None) -> None:
+    """dst [n, width]: row j = the cached row of position lo + j of the request in ``slot``, for positions
+    ``first .. last`` (default: all n); zeros for the others (padding of the run)."""
     _need_cuda(dst, cache, block_table)
     _need(dst.is_contiguous() and dst.dtype == cache.dtype and dst.shape[1] == cache.shape[-1], "latent_gather: dst")
     row = block_table[slot]
+    first = lo if first is None else first
+    last = lo + dst.shape[0] - 1 if last is None else last
     load_library("latent_attn").call(
-        "ll_latent_gather", c_int(_dtype_code(dst)), _ptr(dst), _ptr(cache), _ptr(row), c_int(lo), c_int(dst.shape[0]),
-        c_int(dst.shape[1]), c_int(page_size), c_int(cache.shape[0]), _ptr(status), _stream())
+        "ll_latent_gather", c_int(_dtype_code(dst)), _ptr(dst), _ptr(cache), _ptr(row), c_int(lo), c_int(first),
+        c_int(last), c_int(dst.shape[0]), c_int(dst.shape[1]), c_int(page_size), c_int(cache.shape[0]), _ptr(status),
+        _stream())
 
 
 def latent_masked_softmax(P: torch.Tensor, S: torch.Tensor, H: int, p0: int, lo: int, window: Optional[int],

@@ -137,9 +137,13 @@ class LatentAttention(Mixer):
         for b0 in range(0, count, self.QUERY_BLOCK):
             nb = min(self.QUERY_BLOCK, count - b0)
             p0 = ctx + b0
-            lo = max(0, p0 - self.window + 1) if self.window else 0
-            keys = torch.empty((p0 + nb - lo, KD), dtype=lat.dtype, device=lat.device)
-            ops.latent_gather(keys, cache.k, cache.block_table, slot, lo, cache.page_size, step.status)
+            first = max(0, p0 - self.window + 1) if self.window else 0
+            # the run starts at a multiple of 8 positions and is 8 k rows long (zero rows around the cached ones):
+            # widths that the library's fast kernels take
+            lo = first // 8 * 8
+            keys = torch.empty(((p0 + nb - lo + 7) // 8 * 8, KD), dtype=lat.dtype, device=lat.device)
+            ops.latent_gather(keys, cache.k, cache.block_table, slot, lo, cache.page_size, step.status,
+                              first=first, last=p0 + nb - 1)
             qb = q_full[t0 + b0:t0 + b0 + nb].view(nb * H, KD)
             scores = ops.linear(qb, keys, out_dtype=torch.float32)                       # [nb * H, keys]
             weights = torch.empty(scores.shape, dtype=lat.dtype, device=lat.device)

@@ -77,10 +77,12 @@ class LayerNormF32Residual(Norm):
         deltas = [d for d in (delta if isinstance(delta, (tuple, list)) else (delta,)) if d is not None]
         if len(deltas) > 2:
             raise ValueError("layer_norm_f32: at most two pending outputs can be added in the norm")
-        deltas = [whole_output(d, self.out_dtype) for d in deltas] + [None, None]
+        # one of them may come as float32 partial sums of a product split over its inner dimension
+        partial = next((d for d in deltas if d.dim() == 3), None)
+        deltas = [whole_output(d, self.out_dtype) for d in deltas if d is not partial] + [None, None]
         n = residual.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, residual.shape[1]), dtype=self.out_dtype, device=residual.device)
-        ops.add_layernorm(out, residual, deltas[0], deltas[1], self.weight, self.eps, rows)
+        ops.add_layernorm(out, residual, deltas[0], deltas[1], self.weight, self.eps, rows, partial)
         return out
 
 

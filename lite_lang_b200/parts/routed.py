@@ -79,7 +79,8 @@ class RoutedExperts(FeedForward):
         gates, _idx, _w = self.route(x)
         hidden = ops.linear(x, self.w_up)
         ops.moe_act(hidden, gates, self.shared_ff, self.ff, self.E, self.activation)
-        return ops.linear(hidden, self.w_down)
+        # (few tokens and many hidden units: float32 partial sums of a split inner dimension, added up by the norm)
+        return ops.linear(hidden, self.w_down, partial_ok=True)
 
 
 register_part("feed_forward", "routed_experts", RoutedExperts)

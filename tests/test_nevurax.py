@@ -157,6 +157,14 @@ def test_layer_norm_and_scaled_embedding(dtype):
     assert torch.allclose(h.double(), want_h, atol=1e-5)
     ref = P.layer_norm(want_h.cpu(), w.double().cpu(), 1e-5)
     assert rel_err(out.float().cpu().numpy(), ref.numpy()) <= (1e-5 if dtype == torch.float32 else 1e-2)
+    # a third addend as float32 partial sums of a product that was split over its inner dimension
+    part = torch.randn(3, 4, hidden, generator=g).to(dev())
+    h3, out3 = h.clone(), torch.empty(4, hidden, dtype=dtype, device=dev())
+    ops.add_layernorm(out3, h3, d1, None, w, 1e-5, None, part)
+    want3 = h.double() + (d1.double() + part.sum(0).to(dtype).double())
+    assert torch.allclose(h3.double(), want3, atol=1e-5)
+    assert rel_err(out3.float().cpu().numpy(), P.layer_norm(want3.cpu(), w.double().cpu(), 1e-5).numpy()) <= \
+        (1e-5 if dtype == torch.float32 else 1e-2)
     rows = torch.tensor([2, 0], dtype=torch.int32, device=dev())
     out2 = torch.empty(2, hidden, dtype=dtype, device=dev())
     kept = h.clone()
@@ -412,10 +420,11 @@ def test_routed_experts_part(dtype, E, top, ff, shared):
     assert torch.equal(idx.cpu().long(), ridx)
     assert torch.allclose(wts.double().cpu(), rw, atol=1e-5)
     assert torch.allclose(gates.double().cpu().sum(1), rw.sum(1), atol=1e-5)
-    out = part.forward(xd, None)
+    from lite_lang_b200.parts import whole_output
+    out = whole_output(part.forward(xd, None), dtype)
     assert rel_err(out.float().cpu().numpy(), ref.numpy()) <= (2e-5 if dtype == torch.float32 else 3e-2)
     # a token's result does not depend on its neighbours in the step
-    alone = part.forward(xd[4:5].contiguous(), None)
+    alone = whole_output(part.forward(xd[4:5].contiguous(), None), dtype)
     assert rel_err(alone.float().cpu().numpy(), out[4:5].float().cpu().numpy()) <= (1e-5 if dtype == torch.float32 else 2e-2)
 
 
