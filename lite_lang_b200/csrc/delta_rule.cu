@@ -130,25 +130,34 @@ __global__ void delta_conv_update_kernel(const T* __restrict__ proj, long proj_s
   }
 }
 
-// The scan.  A block of 128 threads owns 16 value columns of one (entry, head); 8 lanes share a column, lane l
-// holding key channels l, l + 8, ... in NR registers.  The tokens' q, k, decay, v and beta come through shared
-// memory in chunks of DR_CH tokens, copied asynchronously (cp.async) a chunk ahead, so that the scan itself waits
-// for memory once a chunk and meets no barrier between the tokens of a chunk.  Sums run in two interleaved chains
-// (even and odd registers) and then over the 8 lanes, in a fixed order.
-#define DR_COLS 16
-#define DR_LANES 8
-#define DR_CH 8
+// The scan.  What bounds it is the chain of dependent operations from one token to the next of a value column, so
+// a column is spread over as many lanes as leave each lane DR_NR = 4 key channels (8 for heads of more than 128
+// channels): two short multiply-add chains and log2(LANES) shuffle steps a sum, all columns of all heads resident
+// at once, and enough warps a scheduler to fill the gaps that one warp's dependent instructions leave (a capture
+// of the 8-channel version showed 0.27 instructions issued a cycle and scheduler with 1.3 warps each).  A block of 128 threads owns 128 / LANES value columns of one (entry, head); lane l holds
+// channels l, l + LANES, ....  The tokens' q, k, decay, v and beta come through shared memory in chunks of DR_CH
+// tokens, copied asynchronously (cp.async) a chunk ahead, so that the scan waits for memory once a chunk and meets
+// no barrier between the tokens of a chunk; rows are padded with zeros to LANES * DR_NR channels so that the inner
+// loops carry no bounds checks.  Sums run in two interleaved chains and then over the lanes, in a fixed order.
+#define DR_THREADS 128
+#define DR_CH 16
 __device__ __forceinline__ void dr_copy4(float* dst_smem, const float* src) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(dst_smem);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
-template <int NR>
-__global__ void __launch_bounds__(DR_COLS * DR_LANES)
+__device__ __forceinline__ void dr_copy16(float* dst_smem, const float* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst_smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+template <int DR_LANES, int DR_NR>
+__global__ void __launch_bounds__(DR_THREADS)
 delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vc,
                         const float* __restrict__ beta, const float* __restrict__ g, float* __restrict__ state,
                         long state_stride, const int* __restrict__ cu_q, const int* __restrict__ req_slot,
                         float* __restrict__ o, DeltaShape s) {
-  extern __shared__ float sm[];   // two buffers of [q | k | decay][DR_CH][dk], v [DR_CH][DR_COLS], beta, head decay [DR_CH]
+  extern __shared__ float sm[];   // two buffers of [q | k | decay][DR_CH][dkp], v [DR_CH][DR_COLS], beta, head decay [DR_CH]
+  constexpr int DR_COLS = DR_THREADS / DR_LANES;
+  constexpr int dkp = DR_LANES * DR_NR;
   LL_PDL_TRIGGER();
   LL_PDL_WAIT();
   const int e = blockIdx.x, h = blockIdx.y;
@@ -166,25 +175,45 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
   const int hk = h / (s.H / s.Hk);
   const int ng = s.per_channel ? s.H * dk : s.H;
   const bool pc = s.per_channel != 0;
-  const int buf_floats = DR_CH * (3 * dk + DR_COLS + 2);
+  constexpr int buf_floats = DR_CH * (3 * dkp + DR_COLS + 2);
+  const bool wide = (dk % 4) == 0 && (Cq % 4) == 0 && (ng % 4 == 0 || !pc) &&
+                    (((uintptr_t)qn | (uintptr_t)kn | (uintptr_t)g) % 16) == 0;
   float* S_ptr = state + (size_t)slot * state_stride + (size_t)h * dk * s.dv;
-  float S[NR];
+  float S[DR_NR];
 #pragma unroll
-  for (int i = 0; i < NR; ++i) {
+  for (int i = 0; i < DR_NR; ++i) {
     const int c = l + DR_LANES * i;
     S[i] = (live_col && c < dk) ? S_ptr[(size_t)c * s.dv + col] : 0.f;
+  }
+  // the padding channels dk .. dkp - 1 of every row: zeros, written once (the copies never touch them)
+  for (int idx = tid; idx < 2 * 3 * DR_CH * (dkp - dk); idx += DR_THREADS) {
+    const int row = idx / (dkp - dk), c = dk + idx % (dkp - dk);
+    const int buf = row / (3 * DR_CH), rr = row % (3 * DR_CH);
+    sm[(size_t)buf * buf_floats + rr * dkp + c] = 0.f;
   }
   auto load_chunk = [&](int t0, int buf) {
     float* b = sm + (size_t)buf * buf_floats;
     const int nt = min(DR_CH, last - t0);
-    for (int idx = tid; idx < nt * dk; idx += DR_COLS * DR_LANES) {
-      const int i = idx / dk, c = idx - i * dk;
-      dr_copy4(b + idx, qn + (size_t)(t0 + i) * Cq + (size_t)hk * dk + c);
-      dr_copy4(b + DR_CH * dk + idx, kn + (size_t)(t0 + i) * Cq + (size_t)hk * dk + c);
-      if (pc) dr_copy4(b + 2 * DR_CH * dk + idx, g + (size_t)(t0 + i) * ng + (size_t)h * dk + c);
+    for (int i = 0; i < nt; ++i) {
+      const float* qs = qn + (size_t)(t0 + i) * Cq + (size_t)hk * dk;
+      const float* ks = kn + (size_t)(t0 + i) * Cq + (size_t)hk * dk;
+      const float* gs = g + (size_t)(t0 + i) * ng + (size_t)h * dk;
+      if (wide) {     // rows of a multiple of four channels at 16-byte addresses: four numbers a copy
+        for (int c = tid * 4; c < dk; c += DR_THREADS * 4) {
+          dr_copy16(b + i * dkp + c, qs + c);
+          dr_copy16(b + (DR_CH + i) * dkp + c, ks + c);
+          if (pc) dr_copy16(b + (2 * DR_CH + i) * dkp + c, gs + c);
+        }
+      } else {
+        for (int c = tid; c < dk; c += DR_THREADS) {
+          dr_copy4(b + i * dkp + c, qs + c);
+          dr_copy4(b + (DR_CH + i) * dkp + c, ks + c);
+          if (pc) dr_copy4(b + (2 * DR_CH + i) * dkp + c, gs + c);
+        }
+      }
     }
-    float* bv = b + 3 * DR_CH * dk;
-    for (int idx = tid; idx < nt * DR_COLS; idx += DR_COLS * DR_LANES) {
+    float* bv = b + 3 * DR_CH * dkp;
+    for (int idx = tid; idx < nt * DR_COLS; idx += DR_THREADS) {
       const int i = idx / DR_COLS, cc = idx % DR_COLS;
       if (col0 + cc < s.dv) dr_copy4(bv + idx, vc + (size_t)(t0 + i) * Cv + (size_t)h * s.dv + col0 + cc);
       else bv[idx] = 0.f;
@@ -207,50 +236,44 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
     }
     __syncthreads();
     const float* b = sm + (size_t)buf * buf_floats;
-    const float* bv = b + 3 * DR_CH * dk;
+    const float* bv = b + 3 * DR_CH * dkp;
     const int nt = min(DR_CH, last - t0);
     for (int i = 0; i < nt; ++i) {
-      const float* sq = b + i * dk;
-      const float* sk = b + DR_CH * dk + i * dk;
-      const float* sg = b + 2 * DR_CH * dk + i * dk;
+      const float* sq = b + i * dkp + l;
+      const float* sk = b + (DR_CH + i) * dkp + l;
+      const float* sg = b + (2 * DR_CH + i) * dkp + l;
       const float v = bv[i * DR_COLS + cl];
       const float bt = bv[DR_CH * DR_COLS + i];
       const float gh = pc ? 1.f : bv[DR_CH * DR_COLS + DR_CH + i];
-      float kr[NR];
+      float kr[DR_NR];
       float d0 = 0.f, d1 = 0.f;
 #pragma unroll
-      for (int j = 0; j < NR; ++j) {
-        const int c = l + DR_LANES * j;
-        kr[j] = c < dk ? sk[c] : 0.f;
-        const float dec = pc ? (c < dk ? sg[c] : 1.f) : gh;
-        S[j] *= dec;
+      for (int j = 0; j < DR_NR; ++j) {
+        kr[j] = sk[DR_LANES * j];
+        S[j] *= pc ? sg[DR_LANES * j] : gh;
         if (j & 1) d1 = fmaf(S[j], kr[j], d1);
         else d0 = fmaf(S[j], kr[j], d0);
       }
       float dot = d0 + d1;
-      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-      dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+#pragma unroll
+      for (int x = 1; x < DR_LANES; x <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, x);
       const float u = bt * (v - dot);
       float o0 = 0.f, o1 = 0.f;
 #pragma unroll
-      for (int j = 0; j < NR; ++j) {
-        const int c = l + DR_LANES * j;
-        const float qv = c < dk ? sq[c] : 0.f;
+      for (int j = 0; j < DR_NR; ++j) {
         S[j] = fmaf(kr[j], u, S[j]);
-        if (j & 1) o1 = fmaf(S[j], qv, o1);
-        else o0 = fmaf(S[j], qv, o0);
+        if (j & 1) o1 = fmaf(S[j], sq[DR_LANES * j], o1);
+        else o0 = fmaf(S[j], sq[DR_LANES * j], o0);
       }
       float oq = o0 + o1;
-      oq += __shfl_xor_sync(0xffffffffu, oq, 1);
-      oq += __shfl_xor_sync(0xffffffffu, oq, 2);
-      oq += __shfl_xor_sync(0xffffffffu, oq, 4);
+#pragma unroll
+      for (int x = 1; x < DR_LANES; x <<= 1) oq += __shfl_xor_sync(0xffffffffu, oq, x);
       if (live_col && l == 0) o[(size_t)(t0 + i) * Cv + (size_t)h * s.dv + col] = oq;
     }
     __syncthreads();   // everyone is done with this buffer before the chunk after the next is copied into it
   }
 #pragma unroll
-  for (int i = 0; i < NR; ++i) {
+  for (int i = 0; i < DR_NR; ++i) {
     const int c = l + DR_LANES * i;
     if (live_col && c < dk) S_ptr[(size_t)c * s.dv + col] = S[i];
   }
@@ -316,20 +339,25 @@ extern "C" int ll_delta_recurrence(const float* qn, const float* kn, const float
   if (num_entries <= 0) return 0;
   if (H <= 0 || Hk <= 0 || H % Hk || dk <= 0 || dk > 256 || dv <= 0) return (int)cudaErrorInvalidValue;
   DeltaShape s{H, Hk, dk, dv, 0, per_channel};
-  dim3 grid(num_entries, H, (dv + DR_COLS - 1) / DR_COLS), block(DR_COLS * DR_LANES);
-  const size_t smem = sizeof(float) * 2 * DR_CH * (3 * (size_t)dk + DR_COLS + 2);
-  if (dk <= 32)
-    ll_launch(delta_recurrence_kernel<4>, grid, block, smem, stream, qn, kn, vc, beta, g, state, state_stride, cu_q,
-              req_slot, o, s);
-  else if (dk <= 64)
-    ll_launch(delta_recurrence_kernel<8>, grid, block, smem, stream, qn, kn, vc, beta, g, state, state_stride, cu_q,
-              req_slot, o, s);
-  else if (dk <= 128)
-    ll_launch(delta_recurrence_kernel<16>, grid, block, smem, stream, qn, kn, vc, beta, g, state, state_stride, cu_q,
-              req_slot, o, s);
-  else
-    ll_launch(delta_recurrence_kernel<32>, grid, block, smem, stream, qn, kn, vc, beta, g, state, state_stride, cu_q,
-              req_slot, o, s);
+#define DR_LAUNCH(LANES, NR)                                                                                        \
+  do {                                                                                                              \
+    constexpr int cols = DR_THREADS / LANES;                                                                        \
+    dim3 grid(num_entries, H, (dv + cols - 1) / cols), block(DR_THREADS);                                           \
+    const size_t smem = sizeof(float) * 2 * DR_CH * (3 * (size_t)LANES * NR + cols + 2);                            \
+    if (smem > 48 * 1024)                                                                                           \
+      cudaFuncSetAttribute(delta_recurrence_kernel<LANES, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
+                           (int)smem);                                                                              \
+    ll_launch(delta_recurrence_kernel<LANES, NR>, grid, block, smem, stream, qn, kn, vc, beta, g, state,            \
+              state_stride, cu_q, req_slot, o, s);                                                                  \
+  } while (0)
+  if (dk <= 4) DR_LAUNCH(1, 4);
+  else if (dk <= 8) DR_LAUNCH(2, 4);
+  else if (dk <= 16) DR_LAUNCH(4, 4);
+  else if (dk <= 32) DR_LAUNCH(8, 4);
+  else if (dk <= 64) DR_LAUNCH(16, 4);
+  else if (dk <= 128) DR_LAUNCH(32, 4);
+  else DR_LAUNCH(32, 8);
+#undef DR_LAUNCH
   return LL_LAUNCH_RESULT();
 }
 

@@ -96,7 +96,8 @@ __global__ void __launch_bounds__(LA_THREADS)
 latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ cache,
                         const int* __restrict__ block_table, int bt_stride, const int* __restrict__ token_req,
                         const int* __restrict__ req_slot, const int* __restrict__ positions, int first, int H, int R,
-                        int r, int page_size, int num_pages, int window, float scale, int* status) {
+                        int r, int page_size, int num_pages, int window, float scale, int* status,
+                        int tiles_per_split, float* __restrict__ part_acc, float* __restrict__ part_ml) {
   extern __shared__ float smem[];
   __shared__ long base_s[LA_TK];
   LL_PDL_TRIGGER();
@@ -116,8 +117,18 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
   const int slot = entry >= 0 ? req_slot[entry] : -1;
   const int p = positions[t];
   T* o_row = out + ((size_t)t * H + h0) * R;
+  // with gridDim.z > 1 the keys of a query are shared out: split z walks tiles_per_split tiles (counted from the
+  // query's first tile) and leaves its running maximum, sum and unnormalised accumulator for the merge kernel
+  const int nsplit = gridDim.z, split = blockIdx.z;
+  float* pa = part_acc ? part_acc + (((size_t)(t - first) * H + h0) * nsplit + split) * R : nullptr;
+  float* pm = part_ml ? part_ml + (((size_t)(t - first) * H + h0) * nsplit + split) * 2 : nullptr;
   if (slot < 0 || p < 0) {
-    for (int i = tid; i < hc * R; i += LA_THREADS) o_row[i] = from_f32<T>(0.f);
+    if (nsplit == 1) {
+      for (int i = tid; i < hc * R; i += LA_THREADS) o_row[i] = from_f32<T>(0.f);
+    } else if (tid < hc) {
+      pm[(size_t)tid * nsplit * 2] = -INFINITY;
+      pm[(size_t)tid * nsplit * 2 + 1] = 0.f;
+    }
     return;
   }
   const int* bt = block_table + (size_t)slot * bt_stride;
@@ -139,7 +150,12 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
   constexpr int VEC = 16 / (int)sizeof(T);
   const bool vec_ok = (KD % VEC) == 0 && ((uintptr_t)cache % 16) == 0;
 
-  for (int tile0 = (lo / LA_TK) * LA_TK; tile0 <= p; tile0 += LA_TK) {
+  int tile_begin = (lo / LA_TK) * LA_TK, tile_end = p;      // first positions of the first and (at most) last tile
+  if (nsplit > 1) {
+    tile_begin += split * tiles_per_split * LA_TK;
+    tile_end = min(p, tile_begin + (tiles_per_split - 1) * LA_TK);
+  }
+  for (int tile0 = tile_begin; tile0 <= tile_end; tile0 += LA_TK) {
     __syncthreads();
     if (tid < LA_TK) {
       const int pos = tile0 + tid;
@@ -257,7 +273,13 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
 #pragma unroll
   for (int i = 0; i < LA_GH / LA_WARPS; ++i) {
     const int g = warp + i * LA_WARPS;
-    if (g < hc && lane == 0) l_s[g] = l_run[i];
+    if (g < hc && lane == 0) {
+      l_s[g] = l_run[i];
+      if (nsplit > 1) {
+        pm[(size_t)g * nsplit * 2] = m_run[i];
+        pm[(size_t)g * nsplit * 2 + 1] = l_run[i];
+      }
+    }
   }
   __syncthreads();
 #pragma unroll
@@ -266,8 +288,36 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
     if (dd < R) {
 #pragma unroll
       for (int g = 0; g < LA_GH; ++g)
-        if (g < hc) o_row[(size_t)g * R + dd] = from_f32<T>(acc[g][c] / l_s[g]);
+        if (g < hc) {
+          if (nsplit == 1) o_row[(size_t)g * R + dd] = from_f32<T>(acc[g][c] / l_s[g]);
+          else pa[(size_t)g * nsplit * R + dd] = acc[g][c];
+        }
     }
+  }
+}
+
+// The splits of a (token, head) put together, in the order of the splits: out = sum_s e^(m_s - M) acc_s /
+// sum_s e^(m_s - M) l_s with M the largest m_s.  One warp per (token, head).
+template <typename T>
+__global__ void latent_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc,
+                                    const float* __restrict__ part_ml, int /*unused*/, int pairs, int R, int nsplit) {
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (pair >= pairs) return;
+  const int lane = threadIdx.x & 31;
+  const float* ml = part_ml + (size_t)pair * nsplit * 2;
+  float M = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ml[2 * s]);
+  float L = 0.f;
+  for (int s = 0; s < nsplit; ++s) L += ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - M) * ml[2 * s + 1];
+  T* o = out + (size_t)pair * R;      // (`out` points at the launch's first token)
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  for (int d = lane; d < R; d += 32) {
+    float a = 0.f;
+    for (int s = 0; s < nsplit; ++s)
+      if (ml[2 * s] != -INFINITY) a = fmaf(expf(ml[2 * s] - M), part_acc[((size_t)pair * nsplit + s) * R + d], a);
+    o[d] = from_f32<T>(a * inv);
   }
 }
 
@@ -335,18 +385,25 @@ extern "C" int ll_latent_prepare(int dtype, const void* proj, long proj_stride, 
 extern "C" int ll_latent_attention(int dtype, void* out, const void* q, const void* cache, const int* block_table,
                                    int bt_stride, const int* token_req, const int* req_slot, const int* positions,
                                    int first, int num_tokens, int H, int R, int r, int page_size, int num_pages,
-                                   int window, float scale, int* status, cudaStream_t stream) {
+                                   int window, float scale, int* status, int nsplit, int tiles_per_split,
+                                   float* part_acc, float* part_ml, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
-  if (H <= 0 || R <= 0 || R > LA_MAX_R || r < 0 || page_size <= 0) return (int)cudaErrorInvalidValue;
+  if (H <= 0 || R <= 0 || R > LA_MAX_R || r < 0 || page_size <= 0 || nsplit < 1) return (int)cudaErrorInvalidValue;
+  if (nsplit > 1 && (tiles_per_split < 1 || part_acc == nullptr || part_ml == nullptr)) return (int)cudaErrorInvalidValue;
   const int KD = R + r;
   const size_t smem = sizeof(float) * ((size_t)LA_GH * KD + (size_t)LA_TK * (KD + 1) + LA_GH * LA_TK + 2 * LA_GH);
-  dim3 grid(num_tokens, (H + LA_GH - 1) / LA_GH);
+  dim3 grid(num_tokens, (H + LA_GH - 1) / LA_GH, nsplit);
   LL_DISPATCH_DTYPE(dtype, {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(latent_attention_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ll_launch(latent_attention_kernel<T>, grid, dim3(LA_THREADS), smem, stream, (T*)out, (const T*)q, (const T*)cache,
               block_table, bt_stride, token_req, req_slot, positions, first, H, R, r, page_size, num_pages, window,
-              scale, status);
+              scale, status, tiles_per_split, part_acc, part_ml);
+    if (nsplit > 1) {
+      const int pairs = num_tokens * H;
+      ll_launch(latent_merge_kernel<T>, dim3((pairs + 3) / 4), dim3(128), 0, stream, (T*)out + (size_t)first * H * R,
+                (const float*)part_acc, (const float*)part_ml, 0, pairs, R, nsplit);
+    }
   });
   return LL_LAUNCH_RESULT();
 }

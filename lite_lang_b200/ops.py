@@ -1089,19 +1089,28 @@ def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, norm_w: torch.Te
 
 def latent_attention(out: torch.Tensor, q_full: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, step,
                      first: int, count: int, H: int, R: int, r: int, page_size: int, window: Optional[int],
-                     scale: float) -> None:
+                     scale: float, nsplit: int = 1, tiles_per_split: int = 0) -> None:
     """Attention in the latent space for tokens ``first .. first + count - 1`` of the step.  ``q_full``
-    [tokens, H, R + r] and ``out`` [tokens, H, R] (sum_j p_j c_j per head) have the cache's dtype."""
+    [tokens, H, R + r] and ``out`` [tokens, H, R] (sum_j p_j c_j per head) have the cache's dtype.
+    ``nsplit`` > 1: every query's keys are shared out over that many CTAs, ``tiles_per_split`` tiles of 32
+    positions each (counted from the query's first visible tile; together they must cover the longest run of
+    keys a query of the step sees), and merged by a second kernel."""
     _need_cuda(out, q_full, cache, block_table)
     _need(q_full.is_contiguous() and out.is_contiguous() and q_full.dtype == cache.dtype == out.dtype
           and tuple(q_full.shape[1:]) == (H, R + r) and tuple(out.shape[1:]) == (H, R), "latent_attention: layouts")
     _need(R <= 512, f"latent_attention: a latent of {R} numbers is wider than the kernel takes (512)")
     _need(0 <= first and first + count <= q_full.shape[0], "latent_attention: token range")
+    part_acc = part_ml = None
+    if nsplit > 1:
+        _need(tiles_per_split >= 1, "latent_attention: splits need tiles_per_split")
+        part_acc = torch.empty((count, H, nsplit, R), dtype=torch.float32, device=out.device)
+        part_ml = torch.empty((count, H, nsplit, 2), dtype=torch.float32, device=out.device)
     load_library("latent_attn").call(
         "ll_latent_attention", c_int(_dtype_code(out)), _ptr(out), _ptr(q_full), _ptr(cache), _ptr(block_table),
         c_int(block_table.stride(0)), _ptr(step.token_req), _ptr(step.req_slot), _ptr(step.positions), c_int(first),
         c_int(count), c_int(H), c_int(R), c_int(r), c_int(page_size), c_int(cache.shape[0]), c_int(window or 0),
-        c_float(scale), _ptr(step.status), _stream())
+        c_float(scale), _ptr(step.status), c_int(nsplit), c_int(tiles_per_split), _ptr(part_acc), _ptr(part_ml),
+        _stream())
 
 
 def latent_gather(dst: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, slot: int, lo: int, page_size: int,

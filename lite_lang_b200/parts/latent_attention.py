@@ -112,12 +112,24 @@ class LatentAttention(Mixer):
         ops.batched_heads(lat.permute(1, 0, 2), self.w_uv_t, out=heads.view(n, H, self.dv).permute(1, 0, 2))
         return ops.linear(heads, self.w_o)
 
+    def _splits(self, n, step, device):
+        """How many CTAs share a query's keys, and how many tiles of 32 positions each takes: few queries with
+        many keys (decode steps) are spread until the CTAs fill the device about once, four tiles a CTA at least.
+        The plan is made for the longest run of keys any query of the step may see (a captured step: of its class
+        of context lengths), so it does not depend on what else is in the batch beyond that bound."""
+        longest = step.max_kv_len if self.window is None else min(step.max_kv_len, self.window)
+        tiles = (longest + 31) // 32 + 1                       # (a run that starts inside a tile touches one more)
+        ctas = n * ((self.H + 7) // 8)
+        nsplit = max(1, min(tiles // 4, ops.sm_count(device) // max(1, ctas), 16))
+        return nsplit, (tiles + nsplit - 1) // nsplit
+
     def attend(self, lat, q_full, step, cache) -> None:
         n, H, R, r = q_full.shape[0], self.H, self.R, self.r
         args = (H, R, r, cache.page_size, self.window, self.scale)
         entries = None if getattr(step, "captured", False) else getattr(step, "entries", None)
         if entries is None or all(len(e.tokens) < self.PRODUCT_MIN_TOKENS for e in entries):
-            ops.latent_attention(lat, q_full, cache.k, cache.block_table, step, 0, n, *args)
+            ops.latent_attention(lat, q_full, cache.k, cache.block_table, step, 0, n, *args,
+                                 *self._splits(n, step, lat.device))
             return
         t, run0 = 0, 0          # run0: first token of the current run of entries that go to the kernel
         for e, ctx in zip(entries, step.entry_ctx):

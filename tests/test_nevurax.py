@@ -339,6 +339,14 @@ def test_latent_attention_windows_and_pages(dtype, page_size, window, H, R, r):
         want = torch.cat([refs[i][c:c + n] for i, c, n in entries])
         err = float((out.double().cpu() - want).abs().max())
         assert err <= tol, (entries, err)
+        # the same with every query's keys shared out over three and over seven CTAs and merged
+        for nsplit in (3, 7):
+            tiles = ((window or 90) + 31) // 32 + 1
+            out2 = torch.full_like(out, float("nan"))
+            ops.latent_attention(out2, q, cache, table, step, 0, q.shape[0], H, R, r, page_size, window, 0.2,
+                                 nsplit, (tiles + nsplit - 1) // nsplit)
+            err = float((out2.double().cpu() - want).abs().max())
+            assert err <= tol, (entries, nsplit, err)
     # the same portion of request 0 by way of products: its run of cached rows copied out of the pages, scores,
     # the masked softmax, the weighted sum; in two blocks of queries, the second starting inside the window's edge
     for c0, n in ((60, 9), (69, 17)):
