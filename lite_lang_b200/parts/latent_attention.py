@@ -114,13 +114,14 @@ class LatentAttention(Mixer):
 
     def _splits(self, n, step, device):
         """How many CTAs share a query's keys, and how many tiles of 32 positions each takes: few queries with
-        many keys (decode steps) are spread until the CTAs fill the device about once, four tiles a CTA at least.
+        many keys (decode steps) are spread until the CTAs fill the device about twice (a tile is a chain of
+        latencies, so a CTA with one or two tiles beats fewer CTAs with more).
         The plan is made for the longest run of keys any query of the step may see (a captured step: of its class
         of context lengths), so it does not depend on what else is in the batch beyond that bound."""
         longest = step.max_kv_len if self.window is None else min(step.max_kv_len, self.window)
         tiles = (longest + 31) // 32 + 1                       # (a run that starts inside a tile touches one more)
         ctas = n * ((self.H + 7) // 8)
-        nsplit = max(1, min(tiles // 4, ops.sm_count(device) // max(1, ctas), 16))
+        nsplit = max(1, min(tiles, (2 * ops.sm_count(device)) // max(1, ctas), 16))
         return nsplit, (tiles + nsplit - 1) // nsplit
 
     def attend(self, lat, q_full, step, cache) -> None:
