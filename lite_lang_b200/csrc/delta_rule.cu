@@ -5,7 +5,8 @@
 // with q, k unit vectors (q also times dk^-1/2), beta in (0, 1) and a decay g in (0, 1] that is
 // one number per head or one per head and key channel.  q, k and v come out of a short causal
 // convolution over time (per channel, `taps` taps, the last one the current token's) and SiLU.
-// A request's record in the state pool is float32 [heads * dk * dv] for S followed by
+// A request's record in the state pool is float32 [heads][dv][dk] for S (a value column's key channels side by
+// side, as the lanes of the scan hold them) followed by
 // [(taps - 1), channels] for the last taps - 1 inputs of the convolutions (oldest first;
 // channels = q | k | v), so that a request can go on in a later step from where it stopped.
 //
@@ -183,7 +184,7 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
 #pragma unroll
   for (int i = 0; i < DR_NR; ++i) {
     const int c = l + DR_LANES * i;
-    S[i] = (live_col && c < dk) ? S_ptr[(size_t)c * s.dv + col] : 0.f;
+    S[i] = (live_col && c < dk) ? S_ptr[(size_t)col * dk + c] : 0.f;
   }
   // the padding channels dk .. dkp - 1 of every row: zeros, written once (the copies never touch them)
   for (int idx = tid; idx < 2 * 3 * DR_CH * (dkp - dk); idx += DR_THREADS) {
@@ -275,7 +276,7 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
 #pragma unroll
   for (int i = 0; i < DR_NR; ++i) {
     const int c = l + DR_LANES * i;
-    if (live_col && c < dk) S_ptr[(size_t)c * s.dv + col] = S[i];
+    if (live_col && c < dk) S_ptr[(size_t)col * dk + c] = S[i];
   }
 }
 

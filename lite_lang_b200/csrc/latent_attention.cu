@@ -297,27 +297,37 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
 }
 
 // The splits of a (token, head) put together, in the order of the splits: out = sum_s e^(m_s - M) acc_s /
-// sum_s e^(m_s - M) l_s with M the largest m_s.  One warp per (token, head).
+// sum_s e^(m_s - M) l_s with M the largest m_s.  One block per (token, head); a thread owns latent numbers
+// tid, tid + 128, ... and asks for all splits' values of a number before it adds them up.
+#define LA_MAX_SPLIT 32
 template <typename T>
-__global__ void latent_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc,
-                                    const float* __restrict__ part_ml, int /*unused*/, int pairs, int R, int nsplit) {
+__global__ void __launch_bounds__(128)
+latent_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                    int pairs, int R, int nsplit) {
+  __shared__ float w_s[LA_MAX_SPLIT];
+  __shared__ float inv_s;
   LL_PDL_TRIGGER();
   LL_PDL_WAIT();
-  const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (pair >= pairs) return;
-  const int lane = threadIdx.x & 31;
+  const int pair = blockIdx.x;
+  const int tid = threadIdx.x;
   const float* ml = part_ml + (size_t)pair * nsplit * 2;
-  float M = -INFINITY;
-  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ml[2 * s]);
-  float L = 0.f;
-  for (int s = 0; s < nsplit; ++s) L += ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - M) * ml[2 * s + 1];
+  if (tid < 32) {
+    float m = tid < nsplit ? ml[2 * tid] : -INFINITY;
+    const float M = warp_max(m);
+    const float w = (tid < nsplit && m != -INFINITY) ? expf(m - M) : 0.f;
+    w_s[tid] = w;
+    float L = 0.f;
+    for (int s = 0; s < nsplit; ++s) L = fmaf(__shfl_sync(0xffffffffu, w, s), ml[2 * s + 1], L);   // split order
+    if (tid == 0) inv_s = L > 0.f ? 1.0f / L : 0.f;
+  }
+  __syncthreads();
   T* o = out + (size_t)pair * R;      // (`out` points at the launch's first token)
-  const float inv = L > 0.f ? 1.0f / L : 0.f;
-  for (int d = lane; d < R; d += 32) {
+  const float* pa = part_acc + (size_t)pair * nsplit * R;
+  for (int d = tid; d < R; d += 128) {
     float a = 0.f;
-    for (int s = 0; s < nsplit; ++s)
-      if (ml[2 * s] != -INFINITY) a = fmaf(expf(ml[2 * s] - M), part_acc[((size_t)pair * nsplit + s) * R + d], a);
-    o[d] = from_f32<T>(a * inv);
+#pragma unroll 8
+    for (int s = 0; s < nsplit; ++s) a = fmaf(w_s[s], pa[(size_t)s * R + d], a);
+    o[d] = from_f32<T>(a * inv_s);
   }
 }
 
@@ -389,7 +399,8 @@ extern "C" int ll_latent_attention(int dtype, void* out, const void* q, const vo
                                    float* part_acc, float* part_ml, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (H <= 0 || R <= 0 || R > LA_MAX_R || r < 0 || page_size <= 0 || nsplit < 1) return (int)cudaErrorInvalidValue;
-  if (nsplit > 1 && (tiles_per_split < 1 || part_acc == nullptr || part_ml == nullptr)) return (int)cudaErrorInvalidValue;
+  if (nsplit > 32 || (nsplit > 1 && (tiles_per_split < 1 || part_acc == nullptr || part_ml == nullptr)))
+    return (int)cudaErrorInvalidValue;
   const int KD = R + r;
   const size_t smem = sizeof(float) * ((size_t)LA_GH * KD + (size_t)LA_TK * (KD + 1) + LA_GH * LA_TK + 2 * LA_GH);
   dim3 grid(num_tokens, (H + LA_GH - 1) / LA_GH, nsplit);
@@ -401,8 +412,8 @@ extern "C" int ll_latent_attention(int dtype, void* out, const void* q, const vo
               scale, status, tiles_per_split, part_acc, part_ml);
     if (nsplit > 1) {
       const int pairs = num_tokens * H;
-      ll_launch(latent_merge_kernel<T>, dim3((pairs + 3) / 4), dim3(128), 0, stream, (T*)out + (size_t)first * H * R,
-                (const float*)part_acc, (const float*)part_ml, 0, pairs, R, nsplit);
+      ll_launch(latent_merge_kernel<T>, dim3(pairs), dim3(128), 0, stream, (T*)out + (size_t)first * H * R,
+                (const float*)part_acc, (const float*)part_ml, pairs, R, nsplit);
     }
   });
   return LL_LAUNCH_RESULT();

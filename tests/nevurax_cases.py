@@ -53,13 +53,15 @@ CASES = {
                        {"type": "latent_attention", "mixer": _latent(2, 16, 32, 48, 24, 4000, 77.0), "mlp": None},
                    ]},
         "seed": 6, "page_size": 16},
-    # a width that is no multiple of 8 (rows of bfloat16 that are not 16-byte aligned), a window of one page
+    # a width that is no multiple of 8 (rows of bfloat16 that are not 16-byte aligned), cached rows of 43 numbers,
+    # a window of one page
     "R": {
         "config": {"architecture": "Nevurax", "vocab": 97, "width": 100, "embedding": {"scale": 4.0},
                    "norm": {"eps": 1e-6},
                    "layers": [
                        {"type": "delta", "mixer": _delta(6, 3, 12, 28, 4), "mlp": _moe(7, 3, 20, 12)},
-                       {"type": "latent_attention", "mixer": _latent(9, 20, 4, 12, 36, 8, 1e6), "mlp": _moe(3, 2, 44, 20)},
+                       {"type": "latent_attention", "mixer": _latent(9, 20, 6, 12, 37, 8, 1e6, dims=4),
+                        "mlp": _moe(3, 2, 44, 20)},
                        {"type": "channel_delta", "mixer": _delta(4, 4, 20, 12, 3, (5, 7)), "mlp": None},
                    ]},
         "seed": 7, "page_size": 8},

@@ -309,7 +309,8 @@ def _latent_reference(rows, q, R, window, scale):
 @gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("page_size,window,H,R,r", [(4, 19, 3, 40, 8), (16, 33, 9, 64, 16), (8, 8, 2, 24, 32),
-                                                    (16, None, 5, 130, 6)])
+                                                    (16, None, 5, 130, 6), (4, 21, 3, 37, 6)])   # (last: rows of 43
+                                                    # numbers, which no 16-byte access fits)
 def test_latent_attention_windows_and_pages(dtype, page_size, window, H, R, r):
     """Prompt portions and single tokens in one launch; a key with a towering score sits at a place that the
     window of some queries just holds and of the next ones just does not."""
