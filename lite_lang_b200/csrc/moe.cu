@@ -184,3 +184,134 @@ extern "C" int ll_moe_act(int dtype, void* h, const float* gates, int num_tokens
   });
   return LL_LAUNCH_RESULT();
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Grouped path (many tokens): the (token, chosen expert) pairs are put in the order of the experts, the rows
+// of the chosen tokens are gathered, and two grouped products (one group an expert, the groups' ends known on
+// the device only) run over them; only the chosen experts' arithmetic is done.
+// ---------------------------------------------------------------------------------------------------------
+
+// One block.  ends [E]: the end of every expert's run of rows; row_token, row_w [pairs + E]: token and routing
+// weight of every row; pair_row [pairs]: the row of pair (t, k).  Every expert's run starts with one row that no
+// pair points at (token 0, weight 0), so that no run is empty: a grouped product does not have to cope with an
+// expert that nobody chose.  Which row inside an expert's run a pair gets is decided by atomics; a row's result
+// does not depend on its place.
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ top_idx, const float* __restrict__ top_w, int pairs, int top, int E,
+                int* __restrict__ ends, int* __restrict__ row_token, float* __restrict__ row_w,
+                int* __restrict__ pair_row) {
+  __shared__ int count[MOE_MAX_E];
+  __shared__ int start[MOE_MAX_E];
+  LL_PDL_WAIT();      // (no early release: what runs next may be a library kernel that does not wait itself)
+  for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 1;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int e = top_idx[p];
+    if (e >= 0 && e < E) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < E; ++e) {
+      row_token[at] = 0;
+      row_w[at] = 0.f;
+      start[e] = at + 1;
+      at += count[e];
+      ends[e] = at;
+    }
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int e = top_idx[p];
+    if (e >= 0 && e < E) {
+      const int row = atomicAdd(&start[e], 1);
+      row_token[row] = p / top;
+      row_w[row] = top_w[p];
+      pair_row[p] = row;
+    } else {
+      pair_row[p] = -1;
+    }
+  }
+}
+
+// dst[row, :] = x[row_token[row], :]
+template <typename T>
+__global__ void moe_gather_rows_kernel(T* __restrict__ dst, const T* __restrict__ x, long x_stride,
+                                       const int* __restrict__ row_token, int hidden) {
+  LL_PDL_WAIT();      // (no early release: what runs next may be a library kernel that does not wait itself)
+  const int row = blockIdx.x;
+  const T* src = x + (size_t)row_token[row] * x_stride;
+  T* d = dst + (size_t)row * hidden;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  if ((hidden % VEC) == 0 && ((uintptr_t)src % 16) == 0 && ((uintptr_t)d % 16) == 0) {
+    for (int i = threadIdx.x; i < hidden / VEC; i += blockDim.x)
+      reinterpret_cast<uint4*>(d)[i] = reinterpret_cast<const uint4*>(src)[i];
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) d[i] = src[i];
+  }
+}
+
+// h[row, :] = act(h[row, :]) * row_w[row], in place
+template <typename T>
+__global__ void moe_row_act_kernel(T* __restrict__ h, const float* __restrict__ row_w, long total, int ff, int act) {
+  LL_PDL_WAIT();      // (no early release: what runs next may be a library kernel that does not wait itself)
+  const long step = (long)gridDim.x * blockDim.x;
+  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += step) {
+    const float w = row_w[idx / ff];
+    h[idx] = from_f32<T>(moe_activation(to_f32<T>(h[idx]), act) * w);
+  }
+}
+
+// out[t, :] = base[t, :] + sum over k (in the order of k) of y[pair_row[t, k], :]; float32 sums, one rounding.
+template <typename T>
+__global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ base, const T* __restrict__ y,
+                                   const int* __restrict__ pair_row, int top, int hidden) {
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float a = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int row = pair_row[(size_t)t * top + k];
+      if (row >= 0) a += to_f32<T>(y[(size_t)row * hidden + c]);
+    }
+    if (base) a += to_f32<T>(base[(size_t)t * hidden + c]);
+    out[(size_t)t * hidden + c] = from_f32<T>(a);
+  }
+}
+
+extern "C" int ll_moe_sort(const int* top_idx, const float* top_w, int num_tokens, int top, int E, int* ends,
+                           int* row_token, float* row_w, int* pair_row, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (E <= 0 || E > MOE_MAX_E || top <= 0) return (int)cudaErrorInvalidValue;
+  ll_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, stream, top_idx, top_w, num_tokens * top, top, E, ends, row_token,
+            row_w, pair_row);
+  return LL_LAUNCH_RESULT();
+}
+
+extern "C" int ll_moe_gather_rows(int dtype, void* dst, const void* x, long x_stride, const int* row_token, int rows,
+                                  int hidden, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  LL_DISPATCH_DTYPE(dtype, ll_launch(moe_gather_rows_kernel<T>, dim3(rows), dim3(128), 0, stream, (T*)dst, (const T*)x,
+                                     x_stride, row_token, hidden));
+  return LL_LAUNCH_RESULT();
+}
+
+extern "C" int ll_moe_row_act(int dtype, void* h, const float* row_w, int rows, int ff, int act, int sms,
+                              cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const long total = (long)rows * ff;
+  const long most = (long)(sms > 0 ? sms : 148) * 16;
+  const long want = (total + 255) / 256;
+  LL_DISPATCH_DTYPE(dtype, ll_launch(moe_row_act_kernel<T>, dim3((int)(want < most ? want : most)), dim3(256), 0, stream,
+                                     (T*)h, row_w, total, ff, act));
+  return LL_LAUNCH_RESULT();
+}
+
+extern "C" int ll_moe_combine(int dtype, void* out, const void* base, const void* y, const int* pair_row,
+                              int num_tokens, int top, int hidden, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  LL_DISPATCH_DTYPE(dtype, ll_launch(moe_combine_kernel<T>, dim3(num_tokens), dim3(256), 0, stream, (T*)out,
+                                     (const T*)base, (const T*)y, pair_row, top, hidden));
+  return LL_LAUNCH_RESULT();
+}

@@ -1191,7 +1191,74 @@ def moe_act(h: torch.Tensor, gates: torch.Tensor, shared_ff: int, ff: int, E: in
     """In place on the first product over all experts' rows: activation times the expert's weight for the token."""
     _need_cuda(h, gates)
     _f32(gates, "gates")
-    _need(h.is_contiguous() and h.shape[1] == shared_ff + E * ff, "moe_act: h is [tokens, shared + experts * ff]")
+    _need(h.stride(1) == 1 and h.stride(0) == h.shape[1] and h.shape[1] == shared_ff + E * ff,
+          "moe_act: h is [tokens, shared + experts * ff]")
     load_library("moe").call("ll_moe_act", c_int(_dtype_code(h)), _ptr(h), _ptr(gates), c_int(h.shape[0]),
                              c_int(shared_ff), c_int(ff), c_int(E), c_int(MOE_ACT[act]), c_int(sm_count(h.device)),
                              _stream())
+
+
+def moe_sort(top_idx: torch.Tensor, top_w: torch.Tensor, E: int):
+    """The (token, chosen expert) pairs in the order of the experts, decided on the device: ``ends`` int32 [E]
+    (end of every expert's run of rows), ``row_token`` int32 and ``row_w`` float32 [pairs + E] (every run starts
+    with a row of weight 0 that no pair points at, so no run is empty), ``pair_row`` int32 [tokens, top] (the row
+    of every pair)."""
+    _need_cuda(top_idx, top_w)
+    _i32(top_idx, "top_idx")
+    _f32(top_w, "top_w")
+    n, top = top_idx.shape
+    dev = top_idx.device
+    ends = torch.empty(E, dtype=torch.int32, device=dev)
+    row_token = torch.empty(n * top + E, dtype=torch.int32, device=dev)
+    row_w = torch.empty(n * top + E, dtype=torch.float32, device=dev)
+    pair_row = torch.empty((n, top), dtype=torch.int32, device=dev)
+    load_library("moe").call("ll_moe_sort", _ptr(top_idx), _ptr(top_w), c_int(n), c_int(top), c_int(E), _ptr(ends),
+                             _ptr(row_token), _ptr(row_w), _ptr(pair_row), _stream())
+    return ends, row_token, row_w, pair_row
+
+
+def moe_gather_rows(x: torch.Tensor, row_token: torch.Tensor) -> torch.Tensor:
+    """[rows, hidden]: x[row_token[row]]."""
+    _need_cuda(x, row_token)
+    _i32(row_token, "row_token")
+    _need(x.stride(1) == 1, "moe_gather_rows: x rows")
+    out = torch.empty((row_token.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+    load_library("moe").call("ll_moe_gather_rows", c_int(_dtype_code(x)), _ptr(out), _ptr(x), c_long(x.stride(0)),
+                             _ptr(row_token), c_int(row_token.numel()), c_int(x.shape[1]), _stream())
+    return out
+
+
+def moe_row_act(h: torch.Tensor, row_w: torch.Tensor, act: str) -> None:
+    """In place: activation of every row times the row's routing weight."""
+    _need_cuda(h, row_w)
+    _f32(row_w, "row_w")
+    _need(h.is_contiguous() and row_w.numel() == h.shape[0], "moe_row_act: layout")
+    load_library("moe").call("ll_moe_row_act", c_int(_dtype_code(h)), _ptr(h), _ptr(row_w), c_int(h.shape[0]),
+                             c_int(h.shape[1]), c_int(MOE_ACT[act]), c_int(sm_count(h.device)), _stream())
+
+
+def moe_combine(base: Optional[torch.Tensor], y: torch.Tensor, pair_row: torch.Tensor) -> torch.Tensor:
+    """[tokens, hidden]: base + the rows of a token's pairs, added in the order of the pairs (float32 sums)."""
+    _need_cuda(base, y, pair_row)
+    _i32(pair_row, "pair_row")
+    n, top = pair_row.shape
+    _need(y.is_contiguous() and (base is None or (base.is_contiguous() and base.dtype == y.dtype
+                                                  and tuple(base.shape) == (n, y.shape[1]))), "moe_combine: layout")
+    out = torch.empty((n, y.shape[1]), dtype=y.dtype, device=y.device)
+    load_library("moe").call("ll_moe_combine", c_int(_dtype_code(y)), _ptr(out), _ptr(base), _ptr(y), _ptr(pair_row),
+                             c_int(n), c_int(top), c_int(y.shape[1]), _stream())
+    return out
+
+
+def grouped_product(rows: torch.Tensor, weights: torch.Tensor, ends: torch.Tensor) -> torch.Tensor:
+    """Library grouped product: rows [total, k] cut into runs that end at ``ends`` [groups] (int32, on the
+    device), run g times weights[g] [n, k] transposed; bfloat16 with float32 accumulation."""
+    _need_cuda(rows, weights, ends)
+    _i32(ends, "ends")
+    _need(rows.dtype == torch.bfloat16 and weights.dtype == torch.bfloat16 and weights.dim() == 3,
+          "grouped_product: bfloat16 rows and weights [groups, n, k]")
+    return torch.nn.functional.grouped_mm(rows, weights.transpose(1, 2), offs=ends)
+
+
+def grouped_product_available() -> bool:
+    return hasattr(torch.nn.functional, "grouped_mm")

@@ -6,10 +6,19 @@ by their scores (divided by their sum first if ``renormalize``).  An expert is d
 act = ``activation`` ("relu2": the square of relu; "silu"; "gelu_tanh").  ``shared_ff`` > 0 adds an expert of
 that width (tensors ``shared.up``, ``shared.down``) that runs for every token with weight 1.
 
-All experts' up matrices are stacked into one (the shared expert's rows first), so the first product is one
-product over all hidden units; the activation kernel multiplies each unit by its expert's weight for the
-token (an exact zero for experts that were not chosen), and one product with the stacked down matrices gives
-the weighted sum.  A token's result does not depend on which other tokens are in the step.
+Two ways through the experts, both without the host ever knowing who chose whom:
+
+* few tokens (decode steps, short portions) and the float32 path: all experts' up matrices are stacked into one
+  (the shared expert's rows first), so the first product is one product over all hidden units; the activation
+  kernel multiplies each unit by its expert's weight for the token (an exact zero for experts that were not
+  chosen), and one product with the stacked down matrices gives the weighted sum.  With few tokens a step reads
+  every expert's weights anyway, and that is what bounds it.
+* many tokens (``GROUPED_MIN_TOKENS``; bfloat16; widths that are multiples of 8): the (token, expert) pairs are
+  put in the order of the experts on the device, the chosen tokens' rows gathered, and two grouped library
+  products (a group an expert, the groups' ends a device array) do only the chosen experts' arithmetic; the
+  pairs' results are added per token in the order of the pairs, onto the shared expert's output.
+
+A token's result does not depend on which other tokens are in the step (beyond which of the two ways it takes).
 """
 
 from __future__ import annotations
@@ -57,6 +66,13 @@ class RoutedExperts(FeedForward):
         self.w_up = torch.cat([u.to(dtype) for u in ups], dim=0).to(device).contiguous()
         self.w_down = torch.cat([w.to(dtype) for w in downs], dim=1).to(device).contiguous()
         self.w_router = fetch("router").to(torch.float32).to(device).contiguous()
+        # views for the grouped way: the experts' up matrices [E, ff, hidden] inside the stacked one; their down
+        # matrices [E, hidden, ff] as strided views of the stacked one's columns
+        sff, ff, E, h = self.shared_ff, self.ff, self.E, self.hidden_size
+        self.w_up_experts = self.w_up[sff:].view(E, ff, h)
+        self.w_down_experts = self.w_down[:, sff:].unflatten(1, (E, ff)).permute(1, 0, 2)
+        self.grouped = (dtype == torch.bfloat16 and h % 8 == 0 and ff % 8 == 0 and sff % 8 == 0
+                        and ops.grouped_product_available())
 
     def weight_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_up, self.w_down, self.w_router))
@@ -75,12 +91,31 @@ class RoutedExperts(FeedForward):
         ops.moe_router(x, self.w_router, gates, top_idx, top_w, self.top, self.score, self.renormalize)
         return gates, top_idx, top_w
 
+    GROUPED_MIN_TOKENS = 128
+
     def forward(self, x, step):
-        gates, _idx, _w = self.route(x)
+        gates, idx, wts = self.route(x)
+        if self.grouped and x.shape[0] >= self.GROUPED_MIN_TOKENS and not getattr(step, "captured", False):
+            return self._forward_grouped(x, idx, wts)
         hidden = ops.linear(x, self.w_up)
         ops.moe_act(hidden, gates, self.shared_ff, self.ff, self.E, self.activation)
         # (few tokens and many hidden units: float32 partial sums of a split inner dimension, added up by the norm)
         return ops.linear(hidden, self.w_down, partial_ok=True)
+
+
+    def _forward_grouped(self, x, idx, wts):
+        sff = self.shared_ff
+        base = None
+        if sff:
+            hs = ops.linear(x, self.w_up[:sff])
+            ops.moe_act(hs, wts, sff, self.ff, 0, self.activation)      # (no routed columns: every weight is 1)
+            base = ops.linear(hs, self.w_down[:, :sff])
+        ends, row_token, row_w, pair_row = ops.moe_sort(idx, wts, self.E)
+        rows = ops.moe_gather_rows(x, row_token)
+        hidden = ops.grouped_product(rows, self.w_up_experts, ends)
+        ops.moe_row_act(hidden, row_w, self.activation)
+        y = ops.grouped_product(hidden, self.w_down_experts, ends)
+        return ops.moe_combine(base, y, pair_row)
 
 
 register_part("feed_forward", "routed_experts", RoutedExperts)

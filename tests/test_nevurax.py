@@ -432,6 +432,15 @@ def test_routed_experts_part(dtype, E, top, ff, shared):
     from lite_lang_b200.parts import whole_output
     out = whole_output(part.forward(xd, None), dtype)
     assert rel_err(out.float().cpu().numpy(), ref.numpy()) <= (2e-5 if dtype == torch.float32 else 3e-2)
+    # many tokens: bfloat16 parts with widths that are multiples of 8 go the grouped way (pairs in the order of the
+    # experts, two grouped products); every token's result is the plain one again, and that of the few-token way
+    many = torch.randn(part.GROUPED_MIN_TOKENS + 37, hidden, generator=g).to(dtype)
+    ref_many = P.moe(many.double(), w64, "mlp.", mlp)
+    assert part.grouped == (dtype == torch.bfloat16 and ff % 8 == 0 and shared % 8 == 0)
+    out_many = whole_output(part.forward(many.to(dev()), None), dtype)
+    assert rel_err(out_many.float().cpu().numpy(), ref_many.numpy()) <= (2e-5 if dtype == torch.float32 else 3e-2)
+    few = whole_output(part.forward(many[:20].to(dev()).contiguous(), None), dtype)
+    assert rel_err(few.float().cpu().numpy(), out_many[:20].float().cpu().numpy()) <= (1e-5 if dtype == torch.float32 else 2e-2)
     # a token's result does not depend on its neighbours in the step
     alone = whole_output(part.forward(xd[4:5].contiguous(), None), dtype)
     assert rel_err(alone.float().cpu().numpy(), out[4:5].float().cpu().numpy()) <= (1e-5 if dtype == torch.float32 else 2e-2)
