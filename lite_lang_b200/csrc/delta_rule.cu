@@ -140,6 +140,8 @@ __global__ void delta_conv_update_kernel(const T* __restrict__ proj, long proj_s
 // tokens, copied asynchronously (cp.async) a chunk ahead, so that the scan waits for memory once a chunk and meets
 // no barrier between the tokens of a chunk; rows are padded with zeros to LANES * DR_NR channels so that the inner
 // loops carry no bounds checks.  Sums run in two interleaved chains and then over the lanes, in a fixed order.
+// The read-out is taken from the state before the token's write plus the write's own share (see the loop), which
+// is the same number as reading the state after the write.
 #define DR_THREADS 128
 #define DR_CH 16
 __device__ __forceinline__ void dr_copy4(float* dst_smem, const float* src) {
@@ -246,29 +248,38 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
       const float v = bv[i * DR_COLS + cl];
       const float bt = bv[DR_CH * DR_COLS + i];
       const float gh = pc ? 1.f : bv[DR_CH * DR_COLS + DR_CH + i];
-      float kr[DR_NR];
-      float d0 = 0.f, d1 = 0.f;
+      // Both sums of a token read the state as the token before left it: with S' = diag(g) S + k u^T,
+      //   S^T (g . k) is what u needs, and o = S'^T q = S^T (g . q) + u (k . q),
+      // so the two reductions over the lanes (and the one of k . q, which does not touch the state) run side
+      // by side, and the chain from token to token is one reduction, not two.
+      float kr[DR_NR], dec[DR_NR];
+      float d0 = 0.f, d1 = 0.f, o0 = 0.f, o1 = 0.f, kq = 0.f;
 #pragma unroll
       for (int j = 0; j < DR_NR; ++j) {
         kr[j] = sk[DR_LANES * j];
-        S[j] *= pc ? sg[DR_LANES * j] : gh;
-        if (j & 1) d1 = fmaf(S[j], kr[j], d1);
-        else d0 = fmaf(S[j], kr[j], d0);
+        dec[j] = pc ? sg[DR_LANES * j] : gh;
+        const float qv = sq[DR_LANES * j];
+        const float gk = dec[j] * kr[j], gq = dec[j] * qv;
+        kq = fmaf(kr[j], qv, kq);
+        if (j & 1) {
+          d1 = fmaf(S[j], gk, d1);
+          o1 = fmaf(S[j], gq, o1);
+        } else {
+          d0 = fmaf(S[j], gk, d0);
+          o0 = fmaf(S[j], gq, o0);
+        }
       }
-      float dot = d0 + d1;
+      float dot = d0 + d1, oq = o0 + o1;
 #pragma unroll
-      for (int x = 1; x < DR_LANES; x <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, x);
+      for (int x = 1; x < DR_LANES; x <<= 1) {
+        dot += __shfl_xor_sync(0xffffffffu, dot, x);
+        oq += __shfl_xor_sync(0xffffffffu, oq, x);
+        kq += __shfl_xor_sync(0xffffffffu, kq, x);
+      }
       const float u = bt * (v - dot);
-      float o0 = 0.f, o1 = 0.f;
+      oq = fmaf(u, kq, oq);
 #pragma unroll
-      for (int j = 0; j < DR_NR; ++j) {
-        S[j] = fmaf(kr[j], u, S[j]);
-        if (j & 1) o1 = fmaf(S[j], sq[DR_LANES * j], o1);
-        else o0 = fmaf(S[j], sq[DR_LANES * j], o0);
-      }
-      float oq = o0 + o1;
-#pragma unroll
-      for (int x = 1; x < DR_LANES; x <<= 1) oq += __shfl_xor_sync(0xffffffffu, oq, x);
+      for (int j = 0; j < DR_NR; ++j) S[j] = fmaf(dec[j], S[j], kr[j] * u);
       if (live_col && l == 0) o[(size_t)(t0 + i) * Cv + (size_t)h * s.dv + col] = oq;
     }
     __syncthreads();   // everyone is done with this buffer before the chunk after the next is copied into it

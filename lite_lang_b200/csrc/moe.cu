@@ -251,14 +251,20 @@ __global__ void moe_gather_rows_kernel(T* __restrict__ dst, const T* __restrict_
   }
 }
 
-// h[row, :] = act(h[row, :]) * row_w[row], in place
-template <typename T>
-__global__ void moe_row_act_kernel(T* __restrict__ h, const float* __restrict__ row_w, long total, int ff, int act) {
+// h[row, :] = act(h[row, :]) * row_w[row], in place; VEC neighbouring numbers of a row a thread
+template <typename T, int VEC>
+__global__ void moe_row_act_kernel(T* __restrict__ h, const float* __restrict__ row_w, long total_vec, int ff, int act) {
   LL_PDL_WAIT();      // (no early release: what runs next may be a library kernel that does not wait itself)
   const long step = (long)gridDim.x * blockDim.x;
-  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += step) {
-    const float w = row_w[idx / ff];
-    h[idx] = from_f32<T>(moe_activation(to_f32<T>(h[idx]), act) * w);
+  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total_vec; idx += step) {
+    const float w = row_w[(idx * VEC) / ff];
+    T v[VEC];
+    if (VEC > 1) *reinterpret_cast<uint4*>(v) = reinterpret_cast<const uint4*>(h)[idx];
+    else v[0] = h[idx];
+#pragma unroll
+    for (int u = 0; u < VEC; ++u) v[u] = from_f32<T>(moe_activation(to_f32<T>(v[u]), act) * w);
+    if (VEC > 1) reinterpret_cast<uint4*>(h)[idx] = *reinterpret_cast<const uint4*>(v);
+    else h[idx] = v[0];
   }
 }
 
@@ -300,11 +306,16 @@ extern "C" int ll_moe_gather_rows(int dtype, void* dst, const void* x, long x_st
 extern "C" int ll_moe_row_act(int dtype, void* h, const float* row_w, int rows, int ff, int act, int sms,
                               cudaStream_t stream) {
   if (rows <= 0) return 0;
-  const long total = (long)rows * ff;
   const long most = (long)(sms > 0 ? sms : 148) * 16;
-  const long want = (total + 255) / 256;
-  LL_DISPATCH_DTYPE(dtype, ll_launch(moe_row_act_kernel<T>, dim3((int)(want < most ? want : most)), dim3(256), 0, stream,
-                                     (T*)h, row_w, total, ff, act));
+  LL_DISPATCH_DTYPE(dtype, {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    const bool wide = (ff % VEC) == 0 && ((uintptr_t)h % 16) == 0;
+    const long total = (long)rows * ff / (wide ? VEC : 1);
+    const long want = (total + 255) / 256;
+    const int blocks = (int)(want < most ? want : most);
+    if (wide) ll_launch(moe_row_act_kernel<T, VEC>, dim3(blocks), dim3(256), 0, stream, (T*)h, row_w, total, ff, act);
+    else ll_launch(moe_row_act_kernel<T, 1>, dim3(blocks), dim3(256), 0, stream, (T*)h, row_w, total, ff, act);
+  });
   return LL_LAUNCH_RESULT();
 }
 
