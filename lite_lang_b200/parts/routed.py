@@ -96,7 +96,13 @@ class RoutedExperts(FeedForward):
     def forward(self, x, step):
         gates, idx, wts = self.route(x)
         if self.grouped and x.shape[0] >= self.GROUPED_MIN_TOKENS and not getattr(step, "captured", False):
-            return self._forward_grouped(x, idx, wts)
+            try:
+                return self._forward_grouped(x, idx, wts)
+            except (RuntimeError, NotImplementedError) as exc:      # a shape the library's grouped product refuses
+                import sys
+                print(f"[lite_lang_b200] routed_experts {self.prefix}: grouped product refused ({str(exc)[:120]}); "
+                      "the stacked way is used instead", file=sys.stderr)
+                self.grouped = False
         hidden = ops.linear(x, self.w_up)
         ops.moe_act(hidden, gates, self.shared_ff, self.ff, self.E, self.activation)
         # (few tokens and many hidden units: float32 partial sums of a split inner dimension, added up by the norm)
