@@ -73,3 +73,77 @@ extern "C" int ll_silu_mul(int dtype, void* out, const void* gate_up, int num_to
                                      (const T*)gate_up, total, inter));
   return LL_LAUNCH_RESULT();
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// The gated product with another activation: out[t, i] = act(gu[t, i]) * gu[t, I + i], act 0 SiLU, 1 ReLU.
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float gate_activation(float g, int act) {
+  return act == 1 ? fmaxf(g, 0.f) : g / (1.0f + expf(-g));
+}
+
+template <typename T>
+__global__ void act_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, long total, int inter, int act) {
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const long idx0 = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long step = (long)gridDim.x * blockDim.x;
+  for (long idx = idx0; idx < total; idx += step) {
+    const long t = idx / inter;
+    const int i = (int)(idx - t * inter);
+    const float g = to_f32<T>(gu[t * 2 * inter + i]);
+    const float u = to_f32<T>(gu[t * 2 * inter + inter + i]);
+    out[idx] = from_f32<T>(gate_activation(g, act) * u);
+  }
+}
+
+extern "C" int ll_act_mul(int dtype, void* out, const void* gate_up, int num_tokens, int inter, int act,
+                          cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (act < 0 || act > 1) return (int)cudaErrorInvalidValue;
+  const long total = (long)num_tokens * inter;
+  const int blocks = (int)min((total + 255) / 256, (long)silu_device_sms() * 16);
+  LL_DISPATCH_DTYPE(dtype, ll_launch(act_mul_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)out,
+                                     (const T*)gate_up, total, inter, act));
+  return LL_LAUNCH_RESULT();
+}
+
+// x[t, i] += bias[i] (float32 sum, rounded once), in place.
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ x, long stride, const float* __restrict__ bias, long total, int width) {
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const long step = (long)gridDim.x * blockDim.x;
+  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += step) {
+    const long t = idx / width;
+    const int i = (int)(idx - t * width);
+    T* p = x + t * stride + i;
+    *p = from_f32<T>(to_f32<T>(*p) + bias[i]);
+  }
+}
+
+extern "C" int ll_add_bias(int dtype, void* x, long stride, const float* bias, int num_tokens, int width,
+                           cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const long total = (long)num_tokens * width;
+  const int blocks = (int)min((total + 255) / 256, (long)silu_device_sms() * 16);
+  LL_DISPATCH_DTYPE(dtype, ll_launch(add_bias_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)x, stride, bias, total,
+                                     width));
+  return LL_LAUNCH_RESULT();
+}
+
+// z <- cap * tanh(z / cap) on float32 logits, in place.
+__global__ void softcap_kernel(float* __restrict__ z, long total, float cap) {
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const long step = (long)gridDim.x * blockDim.x;
+  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += step)
+    z[idx] = cap * tanhf(z[idx] / cap);
+}
+
+extern "C" int ll_softcap(float* z, long total, float cap, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  if (!(cap > 0.f)) return (int)cudaErrorInvalidValue;
+  const int blocks = (int)min((total + 255) / 256, (long)silu_device_sms() * 16);
+  ll_launch(softcap_kernel, dim3(blocks), dim3(256), 0, stream, z, total, cap);
+  return LL_LAUNCH_RESULT();
+}

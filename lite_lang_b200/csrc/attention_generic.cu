@@ -1,5 +1,6 @@
-// Generic paged attention: any number of new tokens per request, any head size
-// up to 256, any page size, any group size, float32 or bfloat16 storage.
+// Generic paged attention: any number of new tokens per request, any key head
+// size up to 256 and value head size up to 512 (the two may differ), any page
+// size, any group size, float32 or bfloat16 storage.
 //
 // It is the kernel of the true 32-bit path and the fallback of the bfloat16
 // path for shapes the tensor-core kernels do not take.  Every new token t of
@@ -22,6 +23,7 @@
 #define AG_WARPS 4
 #define AG_GH 8        // query heads per block
 #define AG_MAX_HD 256
+#define AG_MAX_VD 512
 
 template <typename T>
 __global__ void __launch_bounds__(AG_THREADS)
@@ -29,7 +31,7 @@ paged_attention_generic_kernel(T* __restrict__ out, long out_stride, const T* __
                                const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                                const int* __restrict__ block_table, int bt_stride, const int* __restrict__ token_req,
                                const int* __restrict__ req_slot, const int* __restrict__ positions, int nh, int nkv,
-                               int hd, int page_size, int num_pages, int window, float scale, int* status) {
+                               int hd, int vd, int page_size, int num_pages, int window, float scale, int* status) {
   extern __shared__ float smem[];
   LL_PDL_WAIT();
   LL_PDL_TRIGGER();
@@ -43,17 +45,17 @@ paged_attention_generic_kernel(T* __restrict__ out, long out_stride, const T* __
 
   float* qs = smem;                          // [AG_GH][hd]
   float* ks = qs + AG_GH * hd;               // [AG_TK][hd + 1]
-  float* vs = ks + AG_TK * (hd + 1);         // [AG_TK][hd]
-  float* ps = vs + AG_TK * hd;               // [AG_GH][AG_TK]
+  float* vs = ks + AG_TK * (hd + 1);         // [AG_TK][vd]
+  float* ps = vs + AG_TK * vd;               // [AG_GH][AG_TK]
   float* alpha_s = ps + AG_GH * AG_TK;       // [AG_GH]
   float* l_s = alpha_s + AG_GH;              // [AG_GH]
 
   const int entry = token_req[t];
   const int slot = entry >= 0 ? req_slot[entry] : -1;
   const int p = positions[t];
-  T* o_row = out + (size_t)t * out_stride + (size_t)head0 * hd;
+  T* o_row = out + (size_t)t * out_stride + (size_t)head0 * vd;
   if (slot < 0 || p < 0) {  // padding entry of a captured batch: defined output, no reads
-    for (int i = tid; i < gcount * hd; i += AG_THREADS) o_row[i] = from_f32<T>(0.f);
+    for (int i = tid; i < gcount * vd; i += AG_THREADS) o_row[i] = from_f32<T>(0.f);
     return;
   }
   const int* bt = block_table + (size_t)slot * bt_stride;
@@ -68,11 +70,11 @@ paged_attention_generic_kernel(T* __restrict__ out, long out_stride, const T* __
     m_run[i] = -INFINITY;
     l_run[i] = 0.f;
   }
-  float acc[AG_GH][AG_MAX_HD / AG_THREADS];
+  float acc[AG_GH][AG_MAX_VD / AG_THREADS];
 #pragma unroll
   for (int g = 0; g < AG_GH; ++g)
 #pragma unroll
-    for (int c = 0; c < AG_MAX_HD / AG_THREADS; ++c) acc[g][c] = 0.f;
+    for (int c = 0; c < AG_MAX_VD / AG_THREADS; ++c) acc[g][c] = 0.f;
 
   for (int tile0 = (lo / AG_TK) * AG_TK; tile0 <= p; tile0 += AG_TK) {
     __syncthreads();  // previous tile fully consumed (also orders the q load before the first use)
@@ -80,19 +82,18 @@ paged_attention_generic_kernel(T* __restrict__ out, long out_stride, const T* __
     for (int j = warp; j < AG_TK; j += AG_WARPS) {
       const int pos = tile0 + j;
       const bool valid = (pos >= lo && pos <= p);
-      long base = -1;
+      long base = -1, vbase = -1;
       if (valid) {
         const int page = bt[pos / page_size];
         if (page < 0 || page >= num_pages) {
           if (lane == 0) set_status(status, LL_ERR_PAGE_RANGE);
         } else {
           base = (((long)page * nkv + kvh) * page_size + (pos % page_size)) * hd;
+          vbase = (((long)page * nkv + kvh) * page_size + (pos % page_size)) * vd;
         }
       }
-      for (int d = lane; d < hd; d += 32) {
-        ks[j * (hd + 1) + d] = base >= 0 ? to_f32<T>(k_cache[base + d]) : 0.f;
-        vs[j * hd + d] = base >= 0 ? to_f32<T>(v_cache[base + d]) : 0.f;
-      }
+      for (int d = lane; d < hd; d += 32) ks[j * (hd + 1) + d] = base >= 0 ? to_f32<T>(k_cache[base + d]) : 0.f;
+      for (int d = lane; d < vd; d += 32) vs[j * vd + d] = vbase >= 0 ? to_f32<T>(v_cache[vbase + d]) : 0.f;
     }
     __syncthreads();
     // ---- scores and online softmax: warp w owns heads w, w + 4, ... ; lane = key ----
@@ -121,16 +122,16 @@ paged_attention_generic_kernel(T* __restrict__ out, long out_stride, const T* __
     __syncthreads();
     // ---- accumulate P V: thread owns output columns tid, tid + 128 ----
 #pragma unroll
-    for (int c = 0; c < AG_MAX_HD / AG_THREADS; ++c) {
+    for (int c = 0; c < AG_MAX_VD / AG_THREADS; ++c) {
       const int d = tid + c * AG_THREADS;
-      if (d < hd) {
+      if (d < vd) {
 #pragma unroll
         for (int g = 0; g < AG_GH; ++g) {
           if (g < gcount) {
             float a = acc[g][c] * alpha_s[g];
             const float* pg = ps + g * AG_TK;
 #pragma unroll 8
-            for (int j = 0; j < AG_TK; ++j) a = fmaf(pg[j], vs[j * hd + d], a);
+            for (int j = 0; j < AG_TK; ++j) a = fmaf(pg[j], vs[j * vd + d], a);
             acc[g][c] = a;
           }
         }
@@ -145,19 +146,19 @@ paged_attention_generic_kernel(T* __restrict__ out, long out_stride, const T* __
   }
   __syncthreads();
 #pragma unroll
-  for (int c = 0; c < AG_MAX_HD / AG_THREADS; ++c) {
+  for (int c = 0; c < AG_MAX_VD / AG_THREADS; ++c) {
     const int d = tid + c * AG_THREADS;
-    if (d < hd) {
+    if (d < vd) {
 #pragma unroll
       for (int g = 0; g < AG_GH; ++g)
-        if (g < gcount) o_row[(size_t)g * hd + d] = from_f32<T>(acc[g][c] / l_s[g]);
+        if (g < gcount) o_row[(size_t)g * vd + d] = from_f32<T>(acc[g][c] / l_s[g]);
     }
   }
 }
 
 // q: rows of the step's tokens, head h of token t at q + t*q_stride + h*hd.
-// out: [num_tokens, nh*hd] with row stride out_stride.
-// k_cache / v_cache: one cache plane, each [num_pages, nkv, page_size, hd].
+// out: [num_tokens, nh*vd] with row stride out_stride.
+// k_cache [num_pages, nkv, page_size, hd] and v_cache [num_pages, nkv, page_size, vd]: one cache plane.
 // block_table: int32 [request slots, bt_stride], logical page -> physical page.
 // token_req: int32 [num_tokens] entry of each token; req_slot: int32 [entries]
 // request slot of each entry (-1: padding); positions: int32 [num_tokens].
@@ -165,21 +166,21 @@ paged_attention_generic_kernel(T* __restrict__ out, long out_stride, const T* __
 extern "C" int ll_paged_attention_generic(int dtype, void* out, long out_stride, const void* q, long q_stride,
                                           const void* k_cache, const void* v_cache, const int* block_table,
                                           int bt_stride, const int* token_req, const int* req_slot,
-                                          const int* positions, int num_tokens, int nh, int nkv, int hd,
+                                          const int* positions, int num_tokens, int nh, int nkv, int hd, int vd,
                                           int page_size, int num_pages, int window, float scale, int* status,
                                           cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
-  if (hd <= 0 || hd > AG_MAX_HD || nkv <= 0 || nh % nkv != 0 || page_size <= 0) return (int)cudaErrorInvalidValue;
+  if (hd <= 0 || hd > AG_MAX_HD || vd <= 0 || vd > AG_MAX_VD || nkv <= 0 || nh % nkv != 0 || page_size <= 0) return (int)cudaErrorInvalidValue;
   const int group = nh / nkv;
   const size_t smem =
-      sizeof(float) * ((size_t)AG_GH * hd + (size_t)AG_TK * (hd + 1) + (size_t)AG_TK * hd + AG_GH * AG_TK + 2 * AG_GH);
+      sizeof(float) * ((size_t)AG_GH * hd + (size_t)AG_TK * (hd + 1) + (size_t)AG_TK * vd + AG_GH * AG_TK + 2 * AG_GH);
   dim3 grid(num_tokens, nkv, (group + AG_GH - 1) / AG_GH);
   LL_DISPATCH_DTYPE(dtype, {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(paged_attention_generic_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ll_launch(paged_attention_generic_kernel<T>, grid, dim3(AG_THREADS), smem, stream, (T*)out, out_stride,
               (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, block_table, bt_stride, token_req, req_slot,
-              positions, nh, nkv, hd, page_size, num_pages, window, scale, status);
+              positions, nh, nkv, hd, vd, page_size, num_pages, window, scale, status);
   });
   return LL_LAUNCH_RESULT();
 }

@@ -35,7 +35,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-r
 # name -> (sources, definitions)
 LIBRARIES: Dict[str, Tuple[Tuple[str, ...], Tuple[str, ...]]] = {
     "core": (("embedding.cu", "norm.cu", "layernorm.cu", "rope.cu", "activation.cu", "sampling.cu",
-              "attention_generic.cu"), ()),
+              "attention_generic.cu", "rotate_store.cu", "norm_join.cu"), ()),
     "attn_mma": (("attention_mma.cu", "attention_prefill.cu", "attention_decode.cu"), ()),
     "gemm_smallm": (("gemm_smallm.cu",), ()),
     "gemm_stream": (("gemm_stream.cu",), ()),
@@ -46,6 +46,8 @@ LIBRARIES: Dict[str, Tuple[Tuple[str, ...], Tuple[str, ...]]] = {
     "delta_rule": (("delta_rule.cu",), ()),
     "latent_attn": (("latent_attention.cu",), ()),
     "moe": (("moe.cu",), ()),
+    "streams": (("streams.cu",), ()),
+    "linear_attn": (("linear_attention.cu",), ()),
 }
 
 _INCLUDE = re.compile(r'^\s*#\s*include\s+"([^"]+)"', re.M)

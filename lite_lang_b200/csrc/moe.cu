@@ -14,22 +14,27 @@
 #define MOE_MAX_E 256
 
 // Wr: float32 [E, hidden]; x: T [tokens, hidden]; gates: float32 [tokens, E]; top_idx int32 / top_w float32
-// [tokens, top].  score_fn: 0 softmax, 1 sigmoid.  One block per token: its four warps share out the experts
+// [tokens, top].  score_fn: 0 softmax over all experts, 1 sigmoid, 2 the `top` largest logits are chosen and
+// their weights are the softmax over the chosen logits only.  `bias` (float32 [E], optional) is added to the
+// logits.  With `shared_w` (float32 [tokens]) the router matrix has one more row, the gate of an expert that
+// every token uses: shared_w[t] = sigmoid(Wr[E] . x).  One block per token: its four warps share out the experts
 // (each sum runs over a lane's stride of the row, then over the lanes: an order that depends on the sizes
 // only), then the first warp scores and picks.
 template <typename T>
 __global__ void __launch_bounds__(128)
-moe_router_kernel(const T* __restrict__ x, long x_stride, const float* __restrict__ Wr, float* __restrict__ gates,
-                  int* __restrict__ top_idx, float* __restrict__ top_w, int num_tokens, int hidden, int E, int top,
-                  int score_fn, int renormalize) {
-  __shared__ float z[MOE_MAX_E];
+moe_router_kernel(const T* __restrict__ x, long x_stride, const float* __restrict__ Wr, const float* __restrict__ bias,
+                  float* __restrict__ gates, int* __restrict__ top_idx, float* __restrict__ top_w,
+                  float* __restrict__ shared_w, int num_tokens, int hidden, int E, int top, int score_fn,
+                  int renormalize) {
+  __shared__ float z[MOE_MAX_E + 2];
   LL_PDL_TRIGGER();
   LL_PDL_WAIT();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const T* xr = x + (size_t)t * x_stride;
-  for (int e0 = warp * 2; e0 < E; e0 += 8) {      // two experts a pass: one read of x for two sums
-    const bool two = e0 + 1 < E;
+  const int n_rows = E + (shared_w ? 1 : 0);
+  for (int e0 = warp * 2; e0 < n_rows; e0 += 8) {      // two experts a pass: one read of x for two sums
+    const bool two = e0 + 1 < n_rows;
     const float* w0 = Wr + (size_t)e0 * hidden;
     const float* w1 = Wr + (size_t)(two ? e0 + 1 : e0) * hidden;
     float a0 = 0.f, a1 = 0.f;
@@ -42,13 +47,16 @@ moe_router_kernel(const T* __restrict__ x, long x_stride, const float* __restric
     a0 = warp_sum(a0);
     a1 = warp_sum(a1);
     if (lane == 0) {
-      z[e0] = a0;
-      if (two) z[e0 + 1] = a1;
+      z[e0] = a0 + ((bias && e0 < E) ? bias[e0] : 0.f);
+      if (two) z[e0 + 1] = a1 + ((bias && e0 + 1 < E) ? bias[e0 + 1] : 0.f);
     }
   }
   __syncthreads();
   if (warp != 0) return;
-  if (score_fn == 0) {
+  if (shared_w && lane == 0) shared_w[t] = 1.0f / (1.0f + expf(-z[E]));
+  if (score_fn == 2) {
+    // the logits themselves are compared; the weights are made from the chosen ones below
+  } else if (score_fn == 0) {
     float m = -INFINITY;
     for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
     m = warp_max(m);
@@ -92,6 +100,20 @@ moe_router_kernel(const T* __restrict__ x, long x_stride, const float* __restric
     }
     total += best;
     __syncwarp();
+  }
+  if (score_fn == 2) {
+    // softmax over the chosen logits (the first chosen is the largest), summed in the order they were chosen
+    __syncwarp();
+    const float m = top_w[(size_t)t * top];
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) sum += expf(top_w[(size_t)t * top + k] - m);
+    __syncwarp();
+    for (int k = lane; k < top; k += 32) {
+      const float w = expf(top_w[(size_t)t * top + k] - m) / sum;
+      top_w[(size_t)t * top + k] = w;
+      gr[top_idx[(size_t)t * top + k]] = w;
+    }
+    return;
   }
   if (renormalize && total > 0.f) {
     __syncwarp();
@@ -152,14 +174,14 @@ __global__ void moe_act_kernel(T* __restrict__ h, const float* __restrict__ gate
   }
 }
 
-extern "C" int ll_moe_router(int dtype, const void* x, long x_stride, const float* Wr, float* gates, int* top_idx,
-                             float* top_w, int num_tokens, int hidden, int E, int top, int score_fn, int renormalize,
-                             cudaStream_t stream) {
+extern "C" int ll_moe_router(int dtype, const void* x, long x_stride, const float* Wr, const float* bias, float* gates,
+                             int* top_idx, float* top_w, float* shared_w, int num_tokens, int hidden, int E, int top,
+                             int score_fn, int renormalize, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (E <= 0 || E > MOE_MAX_E || top <= 0 || top > E || hidden <= 0) return (int)cudaErrorInvalidValue;
   LL_DISPATCH_DTYPE(dtype, ll_launch(moe_router_kernel<T>, dim3(num_tokens), dim3(128), 0, stream,
-                                     (const T*)x, x_stride, Wr, gates, top_idx, top_w, num_tokens, hidden, E, top,
-                                     score_fn, renormalize));
+                                     (const T*)x, x_stride, Wr, bias, gates, top_idx, top_w, shared_w, num_tokens,
+                                     hidden, E, top, score_fn, renormalize));
   return LL_LAUNCH_RESULT();
 }
 
@@ -324,5 +346,93 @@ extern "C" int ll_moe_combine(int dtype, void* out, const void* base, const void
   if (num_tokens <= 0) return 0;
   LL_DISPATCH_DTYPE(dtype, ll_launch(moe_combine_kernel<T>, dim3(num_tokens), dim3(256), 0, stream, (T*)out,
                                      (const T*)base, (const T*)y, pair_row, top, hidden));
+  return LL_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Experts with a gate: an expert is down(a * sigmoid(alpha a) * (c + 1)) with a = min(gate x, limit) and
+// c = clamp(up x, -limit, limit).  The first product's rows are, expert by expert, the gate rows then the up
+// rows (an always-on expert's first).
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float clamped_swish_gate(float g, float u, float limit, float alpha) {
+  const float a = fminf(g, limit);
+  const float c = fminf(fmaxf(u, -limit), limit);
+  return a / (1.0f + expf(-alpha * a)) * (c + 1.0f);
+}
+
+// in: T [tokens, 2 * (shared_ff + E * ff)]; out: T [tokens, shared_ff + E * ff] = activation times the
+// expert's weight for the token: gates[t, e] for expert e (zero: not chosen, zeros are written and nothing is
+// read), shared_w[t] (null: 1) for the always-on expert, which has a limit of its own.
+template <typename T>
+__global__ void moe_gated_act_kernel(T* __restrict__ out, const T* __restrict__ in, const float* __restrict__ gates,
+                                     const float* __restrict__ shared_w, int num_tokens, int shared_ff, int ff, int E,
+                                     float limit, float shared_limit, float alpha) {
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const int width = shared_ff + E * ff;
+  const long total = (long)num_tokens * width;
+  const long step = (long)gridDim.x * blockDim.x;
+  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += step) {
+    const int t = (int)(idx / width);
+    const int c = (int)(idx - (long)t * width);
+    const T* row = in + (size_t)t * 2 * width;
+    float w, g, u, lim;
+    if (c < shared_ff) {
+      w = shared_w ? shared_w[t] : 1.f;
+      g = to_f32<T>(row[c]);
+      u = to_f32<T>(row[shared_ff + c]);
+      lim = shared_limit;
+    } else {
+      const int e = (c - shared_ff) / ff;
+      const int j = (c - shared_ff) - e * ff;
+      w = gates[(size_t)t * E + e];
+      if (w == 0.f) {      // an expert that was not chosen contributes an exact zero whatever its first product gave
+        out[idx] = from_f32<T>(0.f);
+        continue;
+      }
+      const T* p = row + 2 * shared_ff + (size_t)e * 2 * ff;
+      g = to_f32<T>(p[j]);
+      u = to_f32<T>(p[ff + j]);
+      lim = limit;
+    }
+    out[idx] = from_f32<T>(clamped_swish_gate(g, u, lim, alpha) * w);
+  }
+}
+
+// in: T [rows, 2 * ff] (gate columns, then up columns); out: T [rows, ff] = activation times row_w[row].
+template <typename T>
+__global__ void moe_row_gated_act_kernel(T* __restrict__ out, const T* __restrict__ in, const float* __restrict__ row_w,
+                                         long total, int ff, float limit, float alpha) {
+  LL_PDL_WAIT();      // (no early release: what runs next may be a library kernel that does not wait itself)
+  const long step = (long)gridDim.x * blockDim.x;
+  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += step) {
+    const long r = idx / ff;
+    const int j = (int)(idx - r * ff);
+    const float w = row_w ? row_w[r] : 1.f;
+    const T* p = in + (size_t)r * 2 * ff;
+    out[idx] = from_f32<T>(clamped_swish_gate(to_f32<T>(p[j]), to_f32<T>(p[ff + j]), limit, alpha) * w);
+  }
+}
+
+extern "C" int ll_moe_gated_act(int dtype, void* out, const void* in, const float* gates, const float* shared_w,
+                                int num_tokens, int shared_ff, int ff, int E, float limit, float shared_limit,
+                                float alpha, int sms, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const long total = (long)num_tokens * (shared_ff + (long)E * ff);
+  if (total <= 0) return (int)cudaErrorInvalidValue;
+  const long most = (long)(sms > 0 ? sms : 148) * 16, want = (total + 255) / 256;
+  LL_DISPATCH_DTYPE(dtype, ll_launch(moe_gated_act_kernel<T>, dim3((int)(want < most ? want : most)), dim3(256), 0,
+                                     stream, (T*)out, (const T*)in, gates, shared_w, num_tokens, shared_ff, ff, E,
+                                     limit, shared_limit, alpha));
+  return LL_LAUNCH_RESULT();
+}
+
+extern "C" int ll_moe_row_gated_act(int dtype, void* out, const void* in, const float* row_w, int rows, int ff,
+                                    float limit, float alpha, int sms, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const long total = (long)rows * ff;
+  const long most = (long)(sms > 0 ? sms : 148) * 16, want = (total + 255) / 256;
+  LL_DISPATCH_DTYPE(dtype, ll_launch(moe_row_gated_act_kernel<T>, dim3((int)(want < most ? want : most)), dim3(256), 0,
+                                     stream, (T*)out, (const T*)in, row_w, total, ff, limit, alpha));
   return LL_LAUNCH_RESULT();
 }

@@ -1,0 +1,93 @@
+// Bias, rotary position encoding with angles made in the kernel, and the write into the paged cache, for a
+// q|k|v projection whose value heads may be wider or narrower than its key heads.
+//
+// Row t of `qkv` holds nh query heads and nkv key heads of hd values, then nkv value heads of vd values.
+//   * bias (float32, optional) is added in float32;
+//   * the first rot_dim values of every q and k head are rotated by angle = float(position) * freq[i], with
+//     freq float32 [rot_dim / 2] (made on the host in float64 and rounded once; any scaling of the positions is
+//     already inside it).  Pair i is (2i, 2i+1) when `interleaved`, (i, i + rot_dim/2) otherwise:
+//     (u, v) -> (u cos a - v sin a, v cos a + u sin a).  cosf and sinf are the accurate ones (no fast math);
+//   * q (and k, v) are written back in place, rounded once; k and v also go to the token's cache slot.
+// No table of positions, so no position is out of range.
+//
+// Cache plane: K [num_pages, nkv, page_size, hd], V [num_pages, nkv, page_size, vd].
+#include "common.cuh"
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+bias_rotate_store_kernel(T* __restrict__ qkv, long qkv_stride, const float* __restrict__ bias,
+                         const int* __restrict__ positions, const float* __restrict__ freq, int rot_dim,
+                         int interleaved, int nh, int nkv, int hd, int vd, const int* __restrict__ slot_map,
+                         T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, long num_slots, int* status) {
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const int t = blockIdx.x;
+  T* row = qkv + (size_t)t * qkv_stride;
+  const float pos = (float)(positions ? positions[t] : 0);
+  long slot = slot_map ? (long)slot_map[t] : -1;
+  if (slot >= num_slots) {
+    if (threadIdx.x == 0) set_status(status, LL_ERR_SLOT_RANGE);
+    slot = -1;
+  }
+  const long page = slot >= 0 ? slot / page_size : 0;
+  const int off = slot >= 0 ? (int)(slot - page * page_size) : 0;
+  const int half = rot_dim >> 1;
+  const int per_head = hd - half;      // work items of a head: `half` pairs + (hd - rot_dim) singles
+  for (int w = threadIdx.x; w < (nh + nkv) * per_head; w += blockDim.x) {
+    const int h = w / per_head;
+    const int i = w - h * per_head;
+    T* head = row + (size_t)h * hd;
+    const float* b = bias ? bias + (size_t)h * hd : nullptr;
+    T* dst = nullptr;
+    if (h >= nh && slot >= 0) dst = k_cache + (((size_t)page * nkv + (h - nh)) * page_size + off) * hd;
+    if (i < half) {
+      const int j0 = interleaved ? 2 * i : i;
+      const int j1 = interleaved ? 2 * i + 1 : i + half;
+      float x0 = to_f32<T>(head[j0]);
+      float x1 = to_f32<T>(head[j1]);
+      if (b) {
+        x0 += b[j0];
+        x1 += b[j1];
+      }
+      const float a = pos * freq[i];
+      const float c = cosf(a), s = sinf(a);
+      const float o0 = x0 * c - x1 * s;
+      const float o1 = x1 * c + x0 * s;
+      head[j0] = from_f32<T>(o0);
+      head[j1] = from_f32<T>(o1);
+      if (dst) {
+        dst[j0] = from_f32<T>(o0);
+        dst[j1] = from_f32<T>(o1);
+      }
+    } else {
+      const int j = rot_dim + (i - half);
+      float x = to_f32<T>(head[j]);
+      if (b) x += b[j];
+      head[j] = from_f32<T>(x);
+      if (dst) dst[j] = from_f32<T>(x);
+    }
+  }
+  const size_t v0 = (size_t)(nh + nkv) * hd;
+  for (int w = threadIdx.x; w < nkv * vd; w += blockDim.x) {
+    const int h = w / vd;
+    const int j = w - h * vd;
+    float x = to_f32<T>(row[v0 + w]);
+    if (bias) {
+      x += bias[v0 + w];
+      row[v0 + w] = from_f32<T>(x);
+    }
+    if (slot >= 0) v_cache[(((size_t)page * nkv + h) * page_size + off) * vd + j] = from_f32<T>(x);
+  }
+}
+
+extern "C" int ll_bias_rotate_store(int dtype, void* qkv, long qkv_stride, const float* bias, const int* positions,
+                                    const float* freq, int rot_dim, int interleaved, int nh, int nkv, int hd, int vd,
+                                    const int* slot_map, void* k_cache, void* v_cache, int page_size, long num_slots,
+                                    int num_tokens, int* status, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || hd <= 0 || vd <= 0) return (int)cudaErrorInvalidValue;
+  LL_DISPATCH_DTYPE(dtype, ll_launch(bias_rotate_store_kernel<T>, dim3(num_tokens), dim3(256), 0, stream, (T*)qkv,
+                                     qkv_stride, bias, positions, freq, rot_dim, interleaved, nh, nkv, hd, vd, slot_map,
+                                     (T*)k_cache, (T*)v_cache, page_size, num_slots, status));
+  return LL_LAUNCH_RESULT();
+}

@@ -57,6 +57,18 @@ class PlannedStep:
         return self._first().writable
 
 
+def _nested(flat: Dict[str, object]) -> Dict[str, object]:
+    """{"mixer.left": a, "mixer.right": b} -> {"mixer": {"left": a, "right": b}}: a composite mixer's members' views."""
+    out: Dict[str, object] = {}
+    for path, view in flat.items():
+        at = out
+        *heads, last = path.split(".")
+        for name in heads:
+            at = at.setdefault(name, {})
+        at[last] = view
+    return out
+
+
 class CausalLM:
     def __init__(self, spec: ModelSpec):
         import lite_lang_b200.parts  # noqa: F401  (registers the built-in parts)
@@ -90,7 +102,7 @@ class CausalLM:
             if rs.cache is not None and not (0 <= rs.cache < i):
                 raise ValueError(f"run order entry {i} reads the cache of entry {rs.cache}, which is not earlier")
             caches: Dict[str, PlannedCache] = {}
-            for role, mixer in self.blocks[rs.layer].mixers():
+            for role, mixer in self.blocks[rs.layer].cache_users():
                 need = mixer.cache_need()
                 if need is None:
                     caches[role] = PlannedCache(None, 0, False)
@@ -154,7 +166,7 @@ class CausalLM:
             self.head.tie(self.embedding.weight)
         for b in self.blocks:
             for _role, mixer in b.mixers():
-                mixer.prepare(device, dtype)
+                mixer.prepare(device, dtype)      # (a composite mixer prepares its members)
 
     def kernel_libraries(self) -> List[str]:
         libs: List[str] = []
@@ -193,6 +205,8 @@ class CausalLM:
                     caches[role] = storage.paged_view(pc.group, pc.plane, step.slot_maps[pc.group], pc.writable)
                 else:
                     caches[role] = storage.state_view(pc.group, pc.plane, pc.writable)
+            if any("." in role for role in caches):
+                caches = _nested(caches)
             h, delta = self.blocks[ps.layer].forward(h, delta, step, caches)
         if step.num_logits == 0:
             return None

@@ -191,27 +191,107 @@ def paged_attention_generic(out: torch.Tensor, q: torch.Tensor, q_stride: int, k
                             v_cache: torch.Tensor, block_table: torch.Tensor, token_req: torch.Tensor,
                             req_slot: torch.Tensor, positions: torch.Tensor, num_tokens: int, num_heads: int,
                             num_kv_heads: int, head_dim: int, page_size: int, window: Optional[int], scale: float,
-                            status: Optional[torch.Tensor]) -> None:
+                            status: Optional[torch.Tensor], value_head_dim: Optional[int] = None) -> None:
     """Attention of every new token over its request's cached keys (any sizes, both dtypes).
 
     ``q`` points at the first query head of the first token; head h of token t
-    is at ``q + t*q_stride + h*head_dim`` (elements).
+    is at ``q + t*q_stride + h*head_dim`` (elements).  ``value_head_dim``: width of a value head
+    (and of an output head) where it differs from the keys'.
     """
+    vd = head_dim if value_head_dim is None else int(value_head_dim)
     _need_cuda(out, q, k_cache, v_cache, block_table, token_req, req_slot, positions)
     for t, nm in ((block_table, "block_table"), (token_req, "token_req"), (req_slot, "req_slot"),
                   (positions, "positions")):
         _i32(t, nm)
-    _need(head_dim <= 256, f"head_dim {head_dim} is larger than the generic attention kernel takes (256)")
+    _need(head_dim <= 256 and vd <= 512, f"heads of {head_dim} keys / {vd} values are larger than the generic "
+          "attention kernel takes (256 / 512)")
     _need(num_heads % num_kv_heads == 0, "num_heads must be a multiple of num_kv_heads")
     _need(out.dtype == q.dtype == k_cache.dtype == v_cache.dtype, "attention: dtypes differ")
-    _need(out.stride(1) == 1 and out.shape[1] == num_heads * head_dim, "attention: out shape")
+    _need(out.stride(1) == 1 and out.shape[1] == num_heads * vd, "attention: out shape")
     _need(k_cache.is_contiguous() and v_cache.is_contiguous(), "cache plane must be contiguous")
-    _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim), "cache plane shape")
+    _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim)
+          and tuple(v_cache.shape[1:]) == (num_kv_heads, page_size, vd), "cache plane shape")
     core().call("ll_paged_attention_generic", c_int(_dtype_code(out)), _ptr(out), c_long(out.stride(0)), _ptr(q),
                 c_long(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), c_int(block_table.stride(0)),
                 _ptr(token_req), _ptr(req_slot), _ptr(positions), c_int(num_tokens), c_int(num_heads),
-                c_int(num_kv_heads), c_int(head_dim), c_int(page_size), c_int(k_cache.shape[0]),
+                c_int(num_kv_heads), c_int(head_dim), c_int(vd), c_int(page_size), c_int(k_cache.shape[0]),
                 c_int(window or 0), c_float(scale), _ptr(status), _stream())
+
+
+def bias_rotate_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: Optional[torch.Tensor],
+                      freq: Optional[torch.Tensor], interleaved: bool, num_heads: int, num_kv_heads: int,
+                      head_dim: int, value_head_dim: int, slot_map: Optional[torch.Tensor],
+                      k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], page_size: int,
+                      status: Optional[torch.Tensor]) -> None:
+    """Bias, rotation of q and k by angles made in the kernel (float32 position x ``freq`` [rot_dim / 2]; pairs
+    (2i, 2i+1) if ``interleaved`` else (i, i + rot_dim/2); the heads' other channels pass), and the store of k and
+    v into a cache plane whose values may be wider or narrower than its keys.  In place on ``qkv``
+    [tokens, (nh + nkv) * head_dim + nkv * value_head_dim]."""
+    _need_cuda(qkv, bias, positions, freq, slot_map, k_cache, v_cache)
+    _f32(bias, "bias")
+    _f32(freq, "freq")
+    _i32(positions, "positions")
+    _i32(slot_map, "slot_map")
+    width = (num_heads + num_kv_heads) * head_dim + num_kv_heads * value_head_dim
+    _need(qkv.dim() == 2 and qkv.shape[1] == width and qkv.stride(1) == 1, "qkv must be [tokens, (nh+nkv)*hd + nkv*vd]")
+    _need(bias is None or bias.numel() == width, "bias size")
+    rot_dim = 0 if freq is None else 2 * freq.numel()
+    _need(rot_dim <= head_dim and (rot_dim == 0 or positions is not None), "rotation: rot_dim <= head_dim, positions")
+    num_slots = 0
+    if slot_map is not None:
+        _need(k_cache is not None and v_cache is not None, "store needs the cache plane")
+        _need(k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype, "cache dtype differs from activations")
+        _need(k_cache.is_contiguous() and v_cache.is_contiguous(), "cache plane must be contiguous")
+        _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim)
+              and tuple(v_cache.shape[1:]) == (num_kv_heads, page_size, value_head_dim), "cache plane shape")
+        num_slots = k_cache.shape[0] * page_size
+    core().call("ll_bias_rotate_store", c_int(_dtype_code(qkv)), _ptr(qkv), c_long(qkv.stride(0)), _ptr(bias),
+                _ptr(positions), _ptr(freq), c_int(rot_dim), c_int(1 if interleaved else 0), c_int(num_heads),
+                c_int(num_kv_heads), c_int(head_dim), c_int(value_head_dim), _ptr(slot_map), _ptr(k_cache),
+                _ptr(v_cache), c_int(page_size), c_long(num_slots), c_int(qkv.shape[0]), _ptr(status), _stream())
+
+
+GATE_ACT = {"silu": 0, "relu": 1}
+
+
+def act_mul(out: torch.Tensor, gate_up: torch.Tensor, act: str) -> None:
+    """out = act(gate) * up for the fused projection [tokens, 2 * I] (gate columns first); act silu or relu."""
+    _need_cuda(out, gate_up)
+    _need(gate_up.is_contiguous() and out.is_contiguous() and out.dtype == gate_up.dtype, "act_mul: layout")
+    n, two_i = gate_up.shape
+    _need(two_i % 2 == 0 and out.shape[0] == n and out.shape[1] == two_i // 2, "act_mul: shapes")
+    core().call("ll_act_mul", c_int(_dtype_code(out)), _ptr(out), _ptr(gate_up), c_int(n), c_int(two_i // 2),
+                c_int(GATE_ACT[act]), _stream())
+
+
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
+    """x[t] += bias in place (float32 sum, one rounding)."""
+    _need_cuda(x, bias)
+    _f32(bias, "bias")
+    _need(x.dim() == 2 and x.stride(1) == 1 and bias.numel() == x.shape[1], "add_bias: shapes")
+    core().call("ll_add_bias", c_int(_dtype_code(x)), _ptr(x), c_long(x.stride(0)), _ptr(bias), c_int(x.shape[0]),
+                c_int(x.shape[1]), _stream())
+
+
+def softcap(logits: torch.Tensor, cap: float) -> None:
+    """logits <- cap * tanh(logits / cap) in place (float32)."""
+    _need_cuda(logits)
+    _f32(logits, "logits")
+    core().call("ll_softcap", _ptr(logits), c_long(logits.numel()), c_float(cap), _stream())
+
+
+def rms_pair_mean(out: torch.Tensor, a: torch.Tensor, bias_a: Optional[torch.Tensor], wa: torch.Tensor,
+                  b: torch.Tensor, wb: torch.Tensor, eps: float) -> None:
+    """out = (rms(a + bias_a) * wa + rms(b) * wb) / 2 row by row: two mixers' outputs joined."""
+    _need_cuda(out, a, bias_a, wa, b, wb)
+    for t, nm in ((bias_a, "bias"), (wa, "weight"), (wb, "weight")):
+        _f32(t, nm)
+    n, width = a.shape
+    _need(tuple(b.shape) == (n, width) and tuple(out.shape) == (n, width) and out.is_contiguous()
+          and a.stride(1) == 1 and b.stride(1) == 1 and a.dtype == b.dtype == out.dtype
+          and wa.numel() == width and wb.numel() == width, "rms_pair_mean: shapes")
+    core().call("ll_rms_pair_mean", c_int(_dtype_code(out)), _ptr(out), _ptr(a), c_long(a.stride(0)), _ptr(bias_a),
+                _ptr(wa), _ptr(b), c_long(b.stride(0)), _ptr(wb), c_float(eps), c_int(n), c_int(width), _stream())
 
 
 def attn_mma_supported(dtype: torch.dtype, head_dim: int, page_size: int, q_stride: int) -> bool:
@@ -1165,26 +1245,65 @@ def product(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
 # --------------------------------------------------------------------------
 # routed feed-forward
 # --------------------------------------------------------------------------
-MOE_SCORE = {"softmax": 0, "sigmoid": 1}
+MOE_SCORE = {"softmax": 0, "sigmoid": 1, "softmax_top": 2}
 MOE_ACT = {"relu2": 0, "silu": 1, "gelu_tanh": 2}
 
 
 def moe_router(x: torch.Tensor, w_router: torch.Tensor, gates: torch.Tensor, top_idx: torch.Tensor,
-               top_w: torch.Tensor, top: int, score: str = "softmax", renormalize: bool = False) -> None:
+               top_w: torch.Tensor, top: int, score: str = "softmax", renormalize: bool = False,
+               bias: Optional[torch.Tensor] = None, shared_w: Optional[torch.Tensor] = None) -> None:
     """Scores over the experts in float32 and the ``top`` largest: ``gates`` float32 [tokens, E] (zero where an
-    expert was not chosen), ``top_idx`` int32 and ``top_w`` float32 [tokens, top]."""
-    _need_cuda(x, w_router, gates, top_idx, top_w)
+    expert was not chosen), ``top_idx`` int32 and ``top_w`` float32 [tokens, top].  ``score`` "softmax_top": the
+    largest logits are chosen and weighted by the softmax over the chosen ones.  ``bias`` float32 [E] is added to
+    the logits.  With ``shared_w`` float32 [tokens], ``w_router`` has one more row and shared_w = sigmoid of it."""
+    _need_cuda(x, w_router, gates, top_idx, top_w, bias, shared_w)
+    _f32(bias, "router bias")
+    _f32(shared_w, "shared_w")
     _f32(w_router, "router weight")
     _f32(gates, "gates")
     _f32(top_w, "top_w")
     _i32(top_idx, "top_idx")
     E, hidden = w_router.shape
+    if shared_w is not None:
+        E -= 1
+    _need(E == gates.shape[1] and (bias is None or bias.numel() == E), "moe_router: experts")
     _need(E <= 256, f"moe_router: {E} experts are more than the kernel takes (256)")
     _need(x.stride(1) == 1 and x.shape[1] == hidden, "moe_router: x rows")
     load_library("moe").call(
-        "ll_moe_router", c_int(_dtype_code(x)), _ptr(x), c_long(x.stride(0)), _ptr(w_router), _ptr(gates),
-        _ptr(top_idx), _ptr(top_w), c_int(x.shape[0]), c_int(hidden), c_int(E), c_int(top), c_int(MOE_SCORE[score]),
-        c_int(1 if renormalize else 0), _stream())
+        "ll_moe_router", c_int(_dtype_code(x)), _ptr(x), c_long(x.stride(0)), _ptr(w_router), _ptr(bias), _ptr(gates),
+        _ptr(top_idx), _ptr(top_w), _ptr(shared_w), c_int(x.shape[0]), c_int(hidden), c_int(E), c_int(top),
+        c_int(MOE_SCORE[score]), c_int(1 if renormalize else 0), _stream())
+
+
+def moe_gated_act(h: torch.Tensor, gates: torch.Tensor, shared_w: Optional[torch.Tensor], shared_ff: int, ff: int,
+                  E: int, limit: float, shared_limit: float, alpha: float) -> torch.Tensor:
+    """[tokens, shared_ff + E * ff] from the first product over all experts' gate and up rows
+    [tokens, 2 * (shared_ff + E * ff)]: a * sigmoid(alpha a) * (c + 1) with a = min(gate, limit),
+    c = clamp(up, -limit, limit), times the expert's weight for the token (``shared_w`` for the always-on one)."""
+    _need_cuda(h, gates, shared_w)
+    _f32(gates, "gates")
+    _f32(shared_w, "shared_w")
+    width = shared_ff + E * ff
+    _need(h.is_contiguous() and h.shape[1] == 2 * width, "moe_gated_act: h is [tokens, 2 * (shared + experts * ff)]")
+    out = torch.empty((h.shape[0], width), dtype=h.dtype, device=h.device)
+    load_library("moe").call("ll_moe_gated_act", c_int(_dtype_code(h)), _ptr(out), _ptr(h), _ptr(gates), _ptr(shared_w),
+                             c_int(h.shape[0]), c_int(shared_ff), c_int(ff), c_int(E), c_float(limit),
+                             c_float(shared_limit), c_float(alpha), c_int(sm_count(h.device)), _stream())
+    return out
+
+
+def moe_row_gated_act(h: torch.Tensor, row_w: Optional[torch.Tensor], limit: float, alpha: float) -> torch.Tensor:
+    """[rows, ff] from [rows, 2 * ff] (gate columns, then up columns): the gated activation times the row's weight."""
+    _need_cuda(h, row_w)
+    _f32(row_w, "row_w")
+    _need(h.is_contiguous() and h.shape[1] % 2 == 0 and (row_w is None or row_w.numel() == h.shape[0]),
+          "moe_row_gated_act: layout")
+    ff = h.shape[1] // 2
+    out = torch.empty((h.shape[0], ff), dtype=h.dtype, device=h.device)
+    load_library("moe").call("ll_moe_row_gated_act", c_int(_dtype_code(h)), _ptr(out), _ptr(h), _ptr(row_w),
+                             c_int(h.shape[0]), c_int(ff), c_float(limit), c_float(alpha), c_int(sm_count(h.device)),
+                             _stream())
+    return out
 
 
 def moe_act(h: torch.Tensor, gates: torch.Tensor, shared_ff: int, ff: int, E: int, act: str) -> None:
@@ -1262,3 +1381,100 @@ def grouped_product(rows: torch.Tensor, weights: torch.Tensor, ends: torch.Tenso
 
 def grouped_product_available() -> bool:
     return hasattr(torch.nn.functional, "grouped_mm")
+
+
+# --------------------------------------------------------------------------
+# a residual of several streams, and the norm that reads it
+# --------------------------------------------------------------------------
+def embed_streams(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, streams: int,
+                  status: Optional[torch.Tensor]) -> None:
+    """out [tokens, streams * hidden] float32: every stream starts as the token's table row."""
+    _need_cuda(out, table, ids)
+    _i32(ids, "ids")
+    _f32(out, "out")
+    hidden = table.shape[1]
+    _need(table.is_contiguous() and out.shape[1] == streams * hidden and out.shape[0] >= ids.numel(),
+          "embed_streams: shapes")
+    load_library("streams").call("ll_embed_streams", c_int(_dtype_code(table)), _ptr(out), _ptr(table), _ptr(ids),
+                                 c_int(ids.numel()), c_int(hidden), c_int(table.shape[0]), c_int(streams),
+                                 _ptr(status), _stream())
+
+
+def stream_tanh_norm(out: torch.Tensor, X: torch.Tensor, streams: int, alpha: torch.Tensor, weight: torch.Tensor,
+                     bias: Optional[torch.Tensor], read: Optional[torch.Tensor] = None,
+                     y: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+                     write: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> None:
+    """One pass over a residual of ``streams`` rows a token (X float32 [tokens, streams * hidden]): a pending
+    sublayer output ``y`` is written back first, X[t] <- sum_s mix[s, t] X[s] + write[t] y (stored unless ``rows``
+    selects rows), then out = tanh(alpha * sum_s read[s] X[s]) * weight + bias in ``out``'s dtype (``read`` None:
+    all ones).  ``y`` may be [tokens, hidden] of out's dtype or float32 partial sums [parts, tokens, hidden]."""
+    _need_cuda(out, X, alpha, weight, bias, read, y, mix, write, rows)
+    for t, nm in ((X, "X"), (alpha, "alpha"), (weight, "weight"), (bias, "bias"), (read, "read"), (mix, "mix"),
+                  (write, "write")):
+        _f32(t, nm)
+    _i32(rows, "rows")
+    hidden = weight.numel()
+    _need(X.dim() == 2 and X.shape[1] == streams * hidden, "stream_tanh_norm: X is [tokens, streams * hidden]")
+    n_out = rows.numel() if rows is not None else X.shape[0]
+    _need(out.is_contiguous() and out.shape[0] >= n_out and out.shape[1] == hidden, "stream_tanh_norm: out shape")
+    _need((mix is None) == (write is None) and (y is None or mix is not None), "stream_tanh_norm: y comes with mix, write")
+    _need(mix is None or (mix.numel() == streams * streams and write.numel() == streams), "stream_tanh_norm: mix, write")
+    _need(read is None or read.numel() == streams, "stream_tanh_norm: read")
+    parts, part_stride, y2, yp = 0, 0, None, None
+    if y is not None and y.dim() == 3:
+        _need(y.dtype == torch.float32 and y.is_contiguous() and tuple(y.shape[1:]) == (X.shape[0], hidden),
+              "stream_tanh_norm: partial sums are float32 [parts, tokens, hidden]")
+        parts, part_stride, yp = y.shape[0], y.shape[1] * hidden, y
+    elif y is not None:
+        _need(y.dtype == out.dtype and y.is_contiguous() and tuple(y.shape) == (X.shape[0], hidden),
+              "stream_tanh_norm: y is [tokens, hidden] of the output's dtype")
+        y2 = y
+    load_library("streams").call(
+        "ll_stream_tanh_norm", c_int(_dtype_code(out)), _ptr(out), _ptr(X), _ptr(y2), _ptr(yp), c_int(parts),
+        c_long(part_stride), _ptr(mix), _ptr(write), _ptr(read), _ptr(alpha), _ptr(weight), _ptr(bias), _ptr(rows),
+        c_int(1 if rows is None else 0), c_int(streams), c_int(hidden), c_int(n_out), _stream())
+
+
+def stream_sum(X: torch.Tensor, streams: int) -> torch.Tensor:
+    """float32 [tokens, hidden]: the sum of a token's streams."""
+    _need_cuda(X)
+    _f32(X, "X")
+    hidden = X.shape[1] // streams
+    out = torch.empty((X.shape[0], hidden), dtype=torch.float32, device=X.device)
+    load_library("streams").call("ll_stream_sum", _ptr(out), _ptr(X), c_int(X.shape[0]), c_int(streams), c_int(hidden),
+                                 _stream())
+    return out
+
+
+# --------------------------------------------------------------------------
+# linear attention with a decay per head
+# --------------------------------------------------------------------------
+def decay_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor, state: torch.Tensor,
+               step, o: torch.Tensor, H: int, dk: int, dv: int, write_state: bool = True) -> None:
+    """S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t for every entry's tokens in order, q, k, v = SiLU of the
+    columns of ``proj`` at the three offsets; ``state`` float32 [slots, H * dv * dk] goes on from where the
+    request stopped; ``o`` float32 [tokens, H * dv]."""
+    _need_cuda(proj, decay, state, o)
+    _f32(decay, "decay")
+    _f32(state, "state")
+    _f32(o, "o")
+    _need(proj.stride(1) == 1 and dk <= 256 and decay.numel() == H and state.shape[1] == H * dk * dv
+          and o.shape[1] == H * dv, "decay_scan: shapes (key heads of at most 256 channels)")
+    load_library("linear_attn").call(
+        "ll_decay_scan", c_int(_dtype_code(proj)), _ptr(proj), c_long(proj.stride(0)), c_int(q_off), c_int(k_off),
+        c_int(v_off), _ptr(decay), _ptr(state), c_long(state.stride(0)), c_int(state.shape[0]), _ptr(step.cu_q),
+        _ptr(step.req_slot), _ptr(o), c_int(step.num_entries), c_int(H), c_int(dk), c_int(dv),
+        c_int(1 if write_state else 0), _ptr(step.status), _stream())
+
+
+def linear_attn_out(y: torch.Tensor, o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, eps: float) -> None:
+    """y = o / rms(o over the whole row) * weight * sigmoid(gate), in y's dtype."""
+    _need_cuda(y, o, weight, gate)
+    _f32(o, "o")
+    _f32(weight, "weight")
+    n, width = o.shape
+    _need(y.is_contiguous() and tuple(y.shape) == (n, width) and gate.stride(1) == 1 and gate.shape[1] == width
+          and gate.dtype == y.dtype and weight.numel() == width, "linear_attn_out: shapes")
+    load_library("linear_attn").call("ll_linear_attn_out", c_int(_dtype_code(y)), _ptr(y), _ptr(o), _ptr(weight),
+                                     _ptr(gate), c_long(gate.stride(0)), c_float(eps), c_int(n), c_int(width),
+                                     _stream())

@@ -22,7 +22,7 @@ import torch
 
 from .. import ops
 from ..config.spec import PartSpec
-from .base import Mixer, NormSplit, PagedKVNeed, TensorDecl, build_part, register_part
+from .base import Mixer, NormSplit, PagedKVNeed, TensorDecl, build_part, register_part, whole_output
 
 
 class GQAttention(Mixer):
@@ -37,39 +37,64 @@ class GQAttention(Mixer):
         self.out_bias = bool(p.get("out_bias", False))
         self.scale = float(p.get("scale", self.head_dim ** -0.5))
         self.window = p.get("window")
+        # ``value_head_dim``: width of a value head where it differs from a key head's (the output projection
+        # then takes num_heads * value_head_dim numbers)
+        self.vdim = int(p.get("value_head_dim") or self.head_dim)
         if self.num_heads % self.num_kv_heads:
             raise ValueError("gqa_attention: num_heads must be a multiple of num_kv_heads")
-        if self.out_bias:
-            raise ValueError("gqa_attention: a bias on the output projection is not built")
         pos = p.get("position")
         self.position = build_part("position", pos) if pos is not None else None
+        self.computed_rotation = bool(getattr(self.position, "computed", False))
+        if self.vdim != self.head_dim and self.position is not None and not self.computed_rotation:
+            raise ValueError("gqa_attention: values wider or narrower than keys go with a position part that makes "
+                             "its angles in the kernel (or none)")
+        # ``tensor_names``: role -> (weight, bias) names under the prefix, for checkpoints that call them otherwise
+        names = {"q": ("q_proj.weight", "q_proj.bias"), "k": ("k_proj.weight", "k_proj.bias"),
+                 "v": ("v_proj.weight", "v_proj.bias"), "o": ("o_proj.weight", "o_proj.bias")}
+        names.update({k: tuple(v) for k, v in dict(p.get("tensor_names") or {}).items()})
+        self.names = names
         self.q_width = self.num_heads * self.head_dim
         self.kv_width = self.num_kv_heads * self.head_dim
+        self.v_width = self.num_kv_heads * self.vdim
+        self.o_width = self.num_heads * self.vdim
         self.w_qkv = None
         self.b_qkv = None
         self.w_o = None
+        self.b_o = None
+        # set by a part that contains this one and adds the output projection's bias in a pass of its own
+        self.defer_out_bias = False
 
     def tensors(self) -> Dict[str, TensorDecl]:
-        h = self.hidden_size
+        h, nm = self.hidden_size, self.names
         d = {
-            "q_proj.weight": TensorDecl((self.q_width, h)),
-            "k_proj.weight": TensorDecl((self.kv_width, h)),
-            "v_proj.weight": TensorDecl((self.kv_width, h)),
-            "o_proj.weight": TensorDecl((h, self.q_width)),
+            nm["q"][0]: TensorDecl((self.q_width, h)),
+            nm["k"][0]: TensorDecl((self.kv_width, h)),
+            nm["v"][0]: TensorDecl((self.v_width, h)),
+            nm["o"][0]: TensorDecl((h, self.o_width)),
         }
         if self.qkv_bias:
-            d["q_proj.bias"] = TensorDecl((self.q_width,), "bias")
-            d["k_proj.bias"] = TensorDecl((self.kv_width,), "bias")
-            d["v_proj.bias"] = TensorDecl((self.kv_width,), "bias")
+            d[nm["q"][1]] = TensorDecl((self.q_width,), "bias")
+            d[nm["k"][1]] = TensorDecl((self.kv_width,), "bias")
+            d[nm["v"][1]] = TensorDecl((self.v_width,), "bias")
+        if self.out_bias:
+            d[nm["o"][1]] = TensorDecl((h,), "bias")
         return d
 
     def load(self, fetch, dtype, device) -> None:
-        w = [fetch(n).to(dtype) for n in ("q_proj.weight", "k_proj.weight", "v_proj.weight")]
+        nm = self.names
+        w = [fetch(nm[r][0]).to(dtype) for r in ("q", "k", "v")]
         self.w_qkv = torch.cat(w, dim=0).to(device).contiguous()
         if self.qkv_bias:
-            b = [fetch(n).to(torch.float32) for n in ("q_proj.bias", "k_proj.bias", "v_proj.bias")]
+            b = [fetch(nm[r][1]).to(torch.float32) for r in ("q", "k", "v")]
             self.b_qkv = torch.cat(b, dim=0).to(device).contiguous()
-        self.w_o = fetch("o_proj.weight").to(dtype).to(device).contiguous()
+        self.w_o = fetch(nm["o"][0]).to(dtype).to(device).contiguous()
+        if self.out_bias:
+            self.b_o = fetch(nm["o"][1]).to(torch.float32).to(device).contiguous()
+
+    @property
+    def deferred_out_bias(self):
+        """The output projection's bias, if a containing part has taken over adding it."""
+        return self.b_o if self.defer_out_bias else None
 
     def weight_bytes(self) -> int:
         n = self.w_qkv.numel() * self.w_qkv.element_size() + self.w_o.numel() * self.w_o.element_size()
@@ -78,13 +103,14 @@ class GQAttention(Mixer):
         return n
 
     def cache_need(self):
-        return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window)
+        return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window,
+                           None if self.vdim == self.head_dim else self.vdim)
 
     def kernel_libraries(self):
         libs = ["core"]
         if self.w_qkv is not None and self.w_qkv.dtype == torch.bfloat16:
             libs.extend(["gemm_smallm", "gemm_stream", "gemm_tc", "gemm_pair"])
-            if self.head_dim in (64, 128):
+            if self.head_dim in (64, 128) and self.vdim == self.head_dim:
                 libs.extend(["attn_mma", "attn_tc"])
         return libs
 
@@ -97,6 +123,12 @@ class GQAttention(Mixer):
     splits_norm = True
 
     def _project_out(self, attn, residual, into_norm=None, status=None):
+        if self.b_o is not None:
+            if self.defer_out_bias:
+                return ops.linear(attn, self.w_o)
+            out = whole_output(ops.linear(attn, self.w_o), attn.dtype)
+            ops.add_bias(out, self.b_o)
+            return out
         if residual is not None and ops.accumulate_preferred(attn, self.w_o):
             ops.linear_accumulate(attn, self.w_o, residual)
             return None
@@ -105,11 +137,21 @@ class GQAttention(Mixer):
             # decode: the o projection adds into the residual stream and leaves the norm after it to the next product
             u, sumsq = ops.gemm_stream_into_norm(attn, self.w_o, residual, into_norm.weight, status)
             return NormSplit(u, sumsq, into_norm.eps)
-        return ops.linear(attn, self.w_o, partial_ok=True)
+        return ops.linear(attn, self.w_o, partial_ok=self.partial_ok)
 
     def forward(self, x, step, cache, residual=None, into_norm=None):
         n = x.shape[0]
         slot_map = cache.slot_map if cache.writable else None
+        if self.computed_rotation or self.vdim != self.head_dim:
+            # angles made in the kernel (no table of positions), and values that may differ in width from the keys
+            qkv = ops.linear(x, self.w_qkv)
+            pos = self.position
+            ops.bias_rotate_store(qkv, self.b_qkv, step.positions, None if pos is None else pos.freq,
+                                  bool(pos is not None and pos.interleaved), self.num_heads, self.num_kv_heads,
+                                  self.head_dim, self.vdim, slot_map, cache.k, cache.v, cache.page_size, step.status)
+            attn = torch.empty((n, self.o_width), dtype=x.dtype, device=x.device)
+            self.attend(attn, qkv, step, cache)
+            return self._project_out(attn, residual, into_norm, step.status)
         if (self.position is not None and self.position.fuses_with_store
                 and ops.qkv_rope_supported(x, self.w_qkv, self.head_dim, self.position.fused_table().shape[1])):
             # decode: projection, bias, rotation and cache write in one kernel; only q is materialised
@@ -204,7 +246,8 @@ class GQAttention(Mixer):
         Single-token entries come first in a step: they go to the decode kernel (keys split over a
         cluster of CTAs), the portions of prompts after them to a prefill kernel (128 query rows a
         CTA share the keys: the tcgen05 one where it takes the shape, else the mma.sync one)."""
-        if ops.attn_mma_supported(qkv.dtype, self.head_dim, cache.page_size, qkv.stride(0)):
+        if self.vdim == self.head_dim and ops.attn_mma_supported(qkv.dtype, self.head_dim, cache.page_size,
+                                                                 qkv.stride(0)):
             n_single = step.num_single
             n_rest = step.num_entries - n_single
             args = (self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size, self.window, self.scale)
@@ -254,7 +297,8 @@ class GQAttention(Mixer):
             return
         ops.paged_attention_generic(out, qkv, qkv.stride(0), cache.k, cache.v, cache.block_table, step.token_req,
                                     step.req_slot, step.positions, qkv.shape[0], self.num_heads, self.num_kv_heads,
-                                    self.head_dim, cache.page_size, self.window, self.scale, step.status)
+                                    self.head_dim, cache.page_size, self.window, self.scale, step.status,
+                                    value_head_dim=self.vdim)
 
 
 register_part("mixer", "gqa_attention", GQAttention)

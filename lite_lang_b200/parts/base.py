@@ -50,6 +50,7 @@ class TensorDecl:
     optional: bool = False
     std: Optional[float] = None
     mean: float = 0.0
+    eye: float = 0.0               # random weights: this much of the identity is added (square matrices)
 
 
 @dataclass(frozen=True)
@@ -188,12 +189,39 @@ class NormSplit(NamedTuple):
     eps: float
 
 
+class StreamWrite(NamedTuple):
+    """A sublayer's output that has not been written into a residual of several streams yet (``parts/streams.py``):
+    X[t] <- sum_s mix[s, t] X[s] + write[t] * y.  The norm that reads the residual next applies it in its pass."""
+    y: torch.Tensor           # [tokens, hidden] in the engine's dtype, or float32 partial sums [parts, tokens, hidden]
+    mix: torch.Tensor         # float32 [streams, streams], indexed [from, to]
+    write: torch.Tensor       # float32 [streams]
+
+
+class Connection(Part):
+    """How a sublayer is joined to the residual: what it reads (``read``: float32 weights over the streams) and how
+    its output goes back (``write(y)`` gives the pending ``StreamWrite``)."""
+
+    kind_family = "connection"
+    read: Optional[torch.Tensor] = None
+
+    def write(self, y) -> "StreamWrite":
+        raise NotImplementedError
+
+
 class Mixer(Part):
     kind_family = "mixer"
 
     def cache_need(self):
         """``PagedKVNeed``, ``StateNeed`` or None."""
         return None
+
+    def sub_mixers(self) -> List[Tuple[str, "Mixer"]]:
+        """The mixers a composite mixer is made of, with their names (empty for an ordinary mixer).  Each gets a
+        cache plane of its own; the composite's ``forward`` is then given a dict name -> cache view."""
+        return []
+
+    # False: ``forward`` must return one [tokens, hidden] tensor, not partial sums (set by a composite on its members)
+    partial_ok = True
 
     def prepare(self, device: torch.device, dtype: torch.dtype) -> None:
         pass
@@ -262,6 +290,22 @@ class Block(Part):
         """The block's mixers with their roles, in the order of ``roles``."""
         return [(role, self.named[role]) for role, family in self.roles.items() if family == "mixer"]
 
+    def cache_users(self) -> List[Tuple[str, "Mixer"]]:
+        """Every mixer that may own memory in the cache manager, by path: ``role`` for an ordinary mixer,
+        ``role.name`` for the members of a composite one."""
+        out: List[Tuple[str, "Mixer"]] = []
+
+        def walk(path: str, m: "Mixer") -> None:
+            subs = m.sub_mixers()
+            if not subs:
+                out.append((path, m))
+            for name, sub in subs:
+                walk(f"{path}.{name}", sub)
+
+        for role, m in self.mixers():
+            walk(role, m)
+        return out
+
     def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], step: "StepView", caches: Mapping[str, Any]):
         raise NotImplementedError
 
@@ -272,6 +316,7 @@ class Block(Part):
 
 _REGISTRY: Dict[str, Dict[str, Any]] = {
     "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {}, "embedding": {}, "head": {},
+    "connection": {},
 }
 
 

@@ -29,6 +29,10 @@ class TokenEmbedding(Part):
         self.scale = float(spec.params.get("scale", 1.0))
         self.residual = str(spec.params.get("residual", "compute"))
         self.tensor = str(spec.params.get("tensor", "weight"))
+        # ``streams``: a residual of several rows a token, [tokens, streams * hidden] float32, all starting as the row
+        self.streams = int(spec.params.get("streams", 1))
+        if self.streams != 1 and (self.residual != "float32" or self.scale != 1.0):
+            raise ValueError("token_embedding: several streams are built for an unscaled float32 residual")
         if self.residual not in ("compute", "float32"):
             raise ValueError(f"token_embedding: residual {self.residual!r} is neither 'compute' nor 'float32'")
         if self.residual == "compute" and self.scale != 1.0:
@@ -41,7 +45,15 @@ class TokenEmbedding(Part):
     def load(self, fetch, dtype, device) -> None:
         self.weight = fetch(self.tensor).to(dtype).to(device).contiguous()
 
+    def kernel_libraries(self):
+        return ("core", "streams") if self.streams != 1 else ("core",)
+
     def forward(self, token_ids: torch.Tensor, num_tokens: int, status) -> torch.Tensor:
+        if self.streams != 1:
+            out = torch.empty((num_tokens, self.streams * self.hidden_size), dtype=torch.float32,
+                              device=self.weight.device)
+            ops.embed_streams(out, self.weight, token_ids[:num_tokens], self.streams, status)
+            return out
         if self.residual == "float32":
             out = torch.empty((num_tokens, self.hidden_size), dtype=torch.float32, device=self.weight.device)
             ops.embed_scaled_f32(out, self.weight, token_ids[:num_tokens], self.scale, status)
@@ -60,6 +72,9 @@ class LMHead(Part):
         self.hidden_size = int(spec.params["hidden_size"])
         self.tied_to = spec.params.get("tied_to")
         self.tensor = str(spec.params.get("tensor", "weight"))
+        # ``softcap`` c: logits <- c * tanh(logits / c)
+        cap = spec.params.get("softcap")
+        self.softcap = float(cap) if cap else None
         self.weight: Optional[torch.Tensor] = None
 
     def tensors(self) -> Dict[str, TensorDecl]:
@@ -74,7 +89,10 @@ class LMHead(Part):
         self.weight = table
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return ops.linear(x, self.weight, out_dtype=torch.float32)
+        logits = ops.linear(x, self.weight, out_dtype=torch.float32)
+        if self.softcap is not None:
+            ops.softcap(logits, self.softcap)
+        return logits
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)

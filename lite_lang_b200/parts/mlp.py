@@ -24,24 +24,28 @@ class GatedMLP(FeedForward):
         self.hidden_size = int(spec.params["hidden_size"])
         self.intermediate_size = int(spec.params["intermediate_size"])
         act = spec.params.get("activation", "silu")
-        if act != "silu":
-            raise ValueError(f"gated_mlp: activation {act!r} is not built (only 'silu')")
+        if act not in ops.GATE_ACT:
+            raise ValueError(f"gated_mlp: activation {act!r} is not built ({', '.join(ops.GATE_ACT)})")
+        self.activation = act
+        # ``tensor_names``: (gate, up, down) under the prefix, for checkpoints that call them otherwise
+        self.names = tuple(spec.params.get("tensor_names") or ("gate_proj.weight", "up_proj.weight",
+                                                               "down_proj.weight"))
         self.w_gate_up = None
         self.w_down = None
 
     def tensors(self) -> Dict[str, TensorDecl]:
         h, i = self.hidden_size, self.intermediate_size
         return {
-            "gate_proj.weight": TensorDecl((i, h)),
-            "up_proj.weight": TensorDecl((i, h)),
-            "down_proj.weight": TensorDecl((h, i)),
+            self.names[0]: TensorDecl((i, h)),
+            self.names[1]: TensorDecl((i, h)),
+            self.names[2]: TensorDecl((h, i)),
         }
 
     def load(self, fetch, dtype, device) -> None:
-        gate = fetch("gate_proj.weight").to(dtype)
-        up = fetch("up_proj.weight").to(dtype)
+        gate = fetch(self.names[0]).to(dtype)
+        up = fetch(self.names[1]).to(dtype)
         self.w_gate_up = torch.cat((gate, up), dim=0).to(device).contiguous()
-        self.w_down = fetch("down_proj.weight").to(dtype).to(device).contiguous()
+        self.w_down = fetch(self.names[2]).to(dtype).to(device).contiguous()
 
     def kernel_libraries(self):
         bf16 = self.w_down is not None and self.w_down.dtype == torch.bfloat16
@@ -54,13 +58,18 @@ class GatedMLP(FeedForward):
     takes_norm_split = True
 
     def accepts_norm_split(self, rows) -> bool:
-        return ops.gated_scaled_supported(rows, self.w_gate_up)
+        return self.activation == "silu" and ops.gated_scaled_supported(rows, self.w_gate_up)
 
     def forward(self, x, step, residual=None):
         if isinstance(x, NormSplit):    # the norm before this part, left to its first product
             act = ops.gemm_stream_gated_scaled(x.scaled, self.w_gate_up, x.sumsq, x.eps, step.status)
-        else:
+        elif self.activation == "silu":
             act = ops.gated_linear(x, self.w_gate_up)
+        else:
+            # (the products with the activation in their epilogue are SiLU ones)
+            gu = ops.linear(x, self.w_gate_up)
+            act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
+            ops.act_mul(act, gu, self.activation)
         if residual is not None and ops.accumulate_preferred(act, self.w_down):
             ops.linear_accumulate(act, self.w_down, residual)
             return None

@@ -12,7 +12,7 @@ from typing import Dict, Optional
 import torch
 
 from .. import ops
-from .base import Norm, TensorDecl, register_part, whole_output
+from .base import Norm, StreamWrite, TensorDecl, register_part, whole_output
 
 
 class RMSNorm(Norm):
@@ -86,5 +86,66 @@ class LayerNormF32Residual(Norm):
         return out
 
 
+class DynamicTanh(Norm):
+    """Dynamic tanh: y = tanh(alpha * u) * w + b with a scalar alpha; no mean, no variance.
+
+    It reads a float32 residual of ``streams`` rows a token, laid out [tokens, streams * hidden]:
+    u = sum_s read[s] X[s] (``read`` None: the plain sum).  ``add_forward`` first applies a pending
+    ``StreamWrite`` (X[t] <- sum_s mix[s, t] X[s] + write[t] y), all in the same pass; with one stream a plain
+    pending output is the residual sum X <- X + y.  The output has the engine's dtype.  Tensors: ``tensor``
+    (w), ``tensor`` + ".b", ``tensor`` + ".alpha" under the prefix.
+    """
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden_size = int(spec.params["hidden_size"])
+        self.streams = int(spec.params.get("streams", 1))
+        self.tensor = str(spec.params.get("tensor", "weight"))
+        if not (1 <= self.streams <= 8):
+            raise ValueError("dynamic_tanh: 1 to 8 streams are built")
+        self.weight: Optional[torch.Tensor] = None
+        self.out_dtype: Optional[torch.dtype] = None
+        self._ones = None
+
+    def tensors(self) -> Dict[str, TensorDecl]:
+        return {self.tensor: TensorDecl((self.hidden_size,), "norm"),
+                self.tensor + ".b": TensorDecl((self.hidden_size,), "bias"),
+                self.tensor + ".alpha": TensorDecl((), "bias", std=0.1, mean=0.6)}
+
+    def load(self, fetch, dtype, device) -> None:
+        self.weight = fetch(self.tensor).to(torch.float32).to(device).contiguous()
+        self.bias = fetch(self.tensor + ".b").to(torch.float32).to(device).contiguous()
+        self.alpha = fetch(self.tensor + ".alpha").to(torch.float32).reshape(1).to(device).contiguous()
+        self.out_dtype = dtype
+        self._ones = torch.ones(1, dtype=torch.float32, device=device)
+
+    def kernel_libraries(self):
+        return ("core", "streams")
+
+    def weight_bytes(self) -> int:
+        return 4 * (2 * self.hidden_size + 1)
+
+    def forward(self, x, out=None):
+        return self.add_forward(x, None)
+
+    def add_forward(self, residual, delta, rows=None, read=None):
+        if residual.dtype != torch.float32 or residual.shape[1] != self.streams * self.hidden_size:
+            raise TypeError("dynamic_tanh: the residual is float32 [tokens, streams * hidden]")
+        y = mix = write = None
+        if isinstance(delta, StreamWrite):
+            y, mix, write = delta
+        elif delta is not None:
+            if self.streams != 1:
+                raise TypeError("dynamic_tanh: a residual of several streams takes a StreamWrite")
+            y, mix, write = delta, self._ones, self._ones
+        if y is not None and y.dim() == 2 and y.dtype != self.out_dtype:
+            y = y.to(self.out_dtype)
+        n = residual.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.hidden_size), dtype=self.out_dtype, device=residual.device)
+        ops.stream_tanh_norm(out, residual, self.streams, self.alpha, self.weight, self.bias, read, y, mix, write, rows)
+        return out
+
+
 register_part("norm", "rms_norm", RMSNorm)
+register_part("norm", "dynamic_tanh", DynamicTanh)
 register_part("norm", "layer_norm_f32", LayerNormF32Residual)

@@ -57,4 +57,38 @@ class RotaryHalfSplit(PositionEncoding):
                             None, None, None, 1, None, num_tokens)
 
 
+class RotaryComputed(PositionEncoding):
+    """Rotary encoding whose angles are made in the kernel: angle = float32(position) * f_i with
+    f_i = theta^(-2i/rotary_dim) / ``position_scale`` (linear scaling of the positions; 1: none), computed in
+    float64 on the host and rounded to float32 once.  No table, so no limit on the positions.  ``layout``:
+    "interleaved" pairs channel 2i with 2i+1, "half_split" pairs i with i + rotary_dim/2; channels from
+    ``rotary_dim`` on pass unchanged.  (u, v) -> (u cos a - v sin a, v cos a + u sin a)."""
+
+    computed = True
+    fuses_with_store = False
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.rot_dim = int(spec.params["rotary_dim"])
+        self.theta = float(spec.params["theta"])
+        self.position_scale = float(spec.params.get("position_scale", 1.0))
+        layout = str(spec.params.get("layout", "interleaved"))
+        if layout not in ("interleaved", "half_split"):
+            raise ValueError(f"rope_computed: layout {layout!r} is neither 'interleaved' nor 'half_split'")
+        if self.rot_dim % 2 or self.rot_dim < 0 or self.position_scale <= 0:
+            raise ValueError("rope_computed: rotary_dim must be even and position_scale positive")
+        self.interleaved = layout == "interleaved"
+        self.freq: Optional[torch.Tensor] = None
+
+    def prepare(self, device) -> None:
+        i = torch.arange(0, self.rot_dim // 2, dtype=torch.float64)
+        f = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / max(self.rot_dim, 1))
+        self.freq = (f / self.position_scale).to(torch.float32).to(device).contiguous() if self.rot_dim else None
+
+    def apply(self, qkv, positions, num_heads, num_kv_heads, head_dim, num_tokens) -> None:
+        ops.bias_rotate_store(qkv[:num_tokens], None, positions, self.freq, self.interleaved, num_heads, num_kv_heads,
+                              head_dim, head_dim, None, None, None, 1, None)
+
+
 register_part("position", "rope_half_split", RotaryHalfSplit)
+register_part("position", "rope_computed", RotaryComputed)

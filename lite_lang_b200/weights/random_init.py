@@ -31,6 +31,8 @@ def draw_tensor(name: str, decl, seed: int, scales: Mapping[str, float], dtype: 
                          "to draw random weights")
     if getattr(decl, "std", None) is not None and decl.role != "table":
         t = decl.mean + decl.std * torch.randn(shape, generator=gen, dtype=torch.float32, device=device)
+        if getattr(decl, "eye", 0.0) and len(shape) == 2 and shape[0] == shape[1]:
+            t = t + decl.eye * torch.eye(shape[0], dtype=torch.float32, device=device)
     elif decl.role == "norm":
         t = 1.0 + scales["norm"] * torch.randn(shape, generator=gen, dtype=torch.float32, device=device)
     elif decl.role == "bias":
