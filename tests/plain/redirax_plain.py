@@ -96,6 +96,14 @@ def rotate_pairs(x: torch.Tensor, positions: torch.Tensor, dims: int, base: floa
 # mixers
 # --------------------------------------------------------------------------
 
+def causal_softmax(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:
+    """One head: q, k [T, d], v [T, dv]; row i sees keys 0..i."""
+    T = q.shape[0]
+    s = (q @ k.T) * scale
+    s = s.masked_fill(torch.arange(T)[None, :] > torch.arange(T)[:, None], float("-inf"))
+    return torch.softmax(s, dim=-1) @ v
+
+
 def softmax_attention(h: torch.Tensor, t: Mapping[str, torch.Tensor], p: str, m: Mapping) -> torch.Tensor:
     T = h.shape[0]
     H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
@@ -110,10 +118,19 @@ def softmax_attention(h: torch.Tensor, t: Mapping[str, torch.Tensor], p: str, m:
     out = torch.zeros(T, H, dv, dtype=F)
     for head in range(H):
         g = head // (H // G)
-        s = (q[:, head] @ k[:, g].T) * float(m["scale"])
-        s = s.masked_fill(pos[None, :] > pos[:, None], float("-inf"))
-        out[:, head] = torch.softmax(s, dim=-1) @ v[:, g]
+        out[:, head] = causal_softmax(q[:, head], k[:, g], v[:, g], float(m["scale"]))
     return out.reshape(T, H * dv) @ t[p + "o"].T + t[p + "o.b"]
+
+
+def decay_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: float,
+                     S: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """One head: q, k [T, d], v [T, dv] -> o [T, dv] and the state after the last token."""
+    S = torch.zeros(q.shape[1], v.shape[1], dtype=F) if S is None else S.clone()
+    o = torch.zeros(q.shape[0], v.shape[1], dtype=F)
+    for i in range(q.shape[0]):
+        S = decay * S + k[i][:, None] * v[i][None, :]
+        o[i] = S.T @ q[i]
+    return o, S
 
 
 def decayed_linear_attention(h: torch.Tensor, t: Mapping[str, torch.Tensor], p: str, m: Mapping,
@@ -125,11 +142,7 @@ def decayed_linear_attention(h: torch.Tensor, t: Mapping[str, torch.Tensor], p: 
     v = silu(h @ t[p + "v"].T).view(T, H, dv)
     o = torch.zeros(T, H, dv, dtype=F)
     for head in range(H):
-        S = torch.zeros(d, dv, dtype=F)
-        decay = float(m["decay"][head])
-        for i in range(T):
-            S = decay * S + k[i, head][:, None] * v[i, head][None, :]
-            o[i, head] = S.T @ q[i, head]
+        o[:, head], _ = decay_recurrence(q[:, head], k[:, head], v[:, head], float(m["decay"][head]))
     o = rms_norm(o.reshape(T, H * dv), t[p + "norm"], eps) * sigmoid(h @ t[p + "g"].T)
     return o @ t[p + "o"].T
 
@@ -148,10 +161,14 @@ def dense_ff(h, t, p):
     return (torch.relu(h @ t[p + "gate"].T) * (h @ t[p + "up"].T)) @ t[p + "down"].T
 
 
+def clamped_gate(g, u, limit: float):
+    a = torch.clamp(g, max=limit)
+    c = torch.clamp(u, min=-limit, max=limit)
+    return a * sigmoid(1.702 * a) * (c + 1.0)
+
+
 def clamped_expert(h, t, p, limit: float):
-    a = torch.clamp(h @ t[p + "gate"].T, max=limit)
-    c = torch.clamp(h @ t[p + "up"].T, min=-limit, max=limit)
-    return (a * sigmoid(1.702 * a) * (c + 1.0)) @ t[p + "down"].T
+    return clamped_gate(h @ t[p + "gate"].T, h @ t[p + "up"].T, limit) @ t[p + "down"].T
 
 
 def route(h, t, p, top: int) -> Tuple[torch.Tensor, torch.Tensor]:

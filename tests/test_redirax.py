@@ -1,0 +1,639 @@
+"""Redirax through the engine against the plain implementation (tests/plain/redirax_plain.py).
+
+CPU: configuration, registry, run order of layers that borrow weights, cache groups, the plain implementation's
+own continuation property.  GPU: each mechanism's kernels alone (with inputs made so that a fault at an edge
+shows), whole prompts, token-by-token decoding through captured steps, portions down to two tokens, mixed
+batches with pages and slots used again, the command-line replay tool and greedy generation through the scheduler.
+"""
+import types
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import TraceRun, rel_err
+from redirax_cases import CASES, write_folder
+from plain import redirax_plain as P
+
+TOL = {torch.float32: 2e-4, torch.bfloat16: 6e-2}
+gpu = pytest.mark.gpu
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def row_errors(got, ref):
+    got, ref = np.asarray(got, dtype=np.float64), np.asarray(ref, dtype=np.float64)
+    assert got.shape == ref.shape, (got.shape, ref.shape)
+    return np.abs(got - ref).max(axis=-1) / np.abs(ref).max(axis=-1)
+
+
+def close(got, ref, dtype) -> bool:
+    """float32: every row within the tolerance.  bfloat16: all but a few rows (two, or 8 %): random weights give a
+    router a near-tie every few dozen tokens, which bfloat16 rounding decides the other way; that moves the row,
+    and through the recurrent state a little of the next ones, by far more than rounding does.  The float32 runs,
+    on the same kernels and cache, allow no such row."""
+    e = row_errors(got, ref)
+    if dtype in (torch.float32, "float32"):
+        return bool(e.max() <= TOL[torch.float32])
+    return int((e > TOL[torch.bfloat16]).sum()) <= max(2, int(0.08 * len(e)))
+
+
+def kernel_tol(dtype):
+    return 2e-5 if dtype == torch.float32 else 1.6e-2
+
+
+# ---------------------------------------------------------------------------------------------------------
+# CPU
+# ---------------------------------------------------------------------------------------------------------
+
+def test_config_registry_and_round_trip():
+    from lite_lang_b200.config import ConfigError, config_from_dict, known_architectures
+    assert "Redirax" in known_architectures()
+    cfg = config_from_dict(CASES["P"]["config"])
+    assert config_from_dict(cfg.to_dict()) == cfg
+    spec = cfg.model_spec()
+    # three layers own tensors (0, 3, 4 of the configuration); five runs; 1 and 2 borrow
+    assert [l.block for l in spec.layers] == ["hyper_pre_norm", "hyper_mixer_only", "hyper_pre_norm"]
+    assert [r.layer for r in spec.order] == [0, 1, 0, 1, 2]
+    assert spec.layers[1].parts["mixer"].prefix == "l3.mix."
+    left = spec.layers[0].parts["mixer"].params["left"]["params"]
+    assert left["value_head_dim"] == 40 and left["scale"] == 0.31 and left["position"].params["position_scale"] == 3.0
+    assert spec.head.params["softcap"] is None
+    assert config_from_dict(CASES["Q"]["config"]).model_spec().head.params["softcap"] == 12.0
+    bad = cfg.to_dict()
+    bad["layers"][0]["type"] = "serial"
+    with pytest.raises(ConfigError):
+        config_from_dict(bad)
+    bad = cfg.to_dict()
+    bad["layers"][0]["mixer"]["right"]["decay"] = [0.5]
+    with pytest.raises(ConfigError):
+        config_from_dict(bad)
+    bad = cfg.to_dict()
+    bad["layers"][1]["weights_of"] = 2       # 2 borrows from 0, fine; make a circle instead
+    bad["layers"][3]["weights_of"] = 1
+    bad["layers"][1]["weights_of"] = 3
+    with pytest.raises(ConfigError):
+        config_from_dict(bad)
+
+
+def test_cache_groups_and_declared_tensors():
+    from lite_lang_b200.config import config_from_dict
+    from lite_lang_b200.engine.model import CausalLM
+    model = CausalLM(config_from_dict(CASES["P"]["config"]).model_spec())
+    kinds = [(g.kind, g.planes) for g in model.cache_groups]
+    # every run has planes of its own, also the runs that borrow weights: two kinds of attention (wide and
+    # narrow values) and two kinds of state record
+    assert sorted(kinds) == [("paged", 2), ("paged", 3), ("state", 2), ("state", 3)]
+    paged = [g for g in model.cache_groups if g.kind == "paged"]
+    assert sorted((g.head_dim, g.value_dim) for g in paged) == [(16, 8), (24, 40)]
+    assert all(pc.writable for ps in model.plan for pc in ps.caches.values())
+    assert [sorted(ps.caches) for ps in model.plan][0] == ["mixer.left", "mixer.right"]
+    names = set(model.declared_tensors())
+    for n in ("embed", "head", "final.norm", "final.norm.alpha", "final.norm.b", "l0.hc1.mix", "l0.hc2.in",
+              "l0.mix.left.q.b", "l0.mix.left.o.b", "l0.mix.left.out", "l0.mix.right.norm", "l0.mix.right.g",
+              "l0.mlp.router.b", "l0.mlp.e3.gate", "l3.mix.right.out", "l4.mlp.gate", "l4.norm2.alpha"):
+        assert n in names, n
+    assert not any(n.startswith(("l1.", "l2.")) for n in names)           # borrowed layers own nothing
+    assert "l3.hc2.in" not in names and "l0.mlp.shared.sg" not in names   # no feed-forward; no shared expert
+    q = CausalLM(config_from_dict(CASES["Q"]["config"]).model_spec()).declared_tensors()
+    assert q["l0.mlp.shared.sg"].shape == (1, 128) and q["l0.mlp.shared.gate"].shape == (48, 128)
+
+
+def test_plain_recurrence_continues_from_a_state_and_streams_of_one_are_a_residual_sum():
+    g = torch.Generator().manual_seed(0)
+    T, dk, dv = 23, 6, 5
+    q, k, v = (torch.randn(T, d, generator=g, dtype=P.F) for d in (dk, dk, dv))
+    whole, S = P.decay_recurrence(q, k, v, 0.9)
+    a, Sa = P.decay_recurrence(q[:9], k[:9], v[:9], 0.9)
+    b, Sb = P.decay_recurrence(q[9:], k[9:], v[9:], 0.9, Sa)
+    assert torch.allclose(torch.cat([a, b]), whole, atol=1e-12) and torch.allclose(S, Sb, atol=1e-12)
+    # the closed form: o_t = sum_{j<=t} decay^(t-j) (q_t . k_j) v_j
+    t = 11
+    want = sum(0.9 ** (t - j) * float(q[t] @ k[j]) * v[j] for j in range(t + 1))
+    assert torch.allclose(whole[t], want, atol=1e-12)
+    X = torch.randn(1, 4, 7, generator=g, dtype=P.F)
+    w = {"n": torch.ones(7, dtype=P.F), "n.b": torch.zeros(7, dtype=P.F), "n.alpha": torch.tensor(0.5, dtype=P.F),
+         "h.in": torch.ones(1, dtype=P.F), "h.out": torch.ones(1, dtype=P.F), "h.mix": torch.ones(1, 1, dtype=P.F)}
+    out = P.stream_sublayer(X, lambda h: 2 * h, w, "n", "h.")
+    assert torch.allclose(out, X + 2 * torch.tanh(0.5 * X), atol=1e-12)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# GPU: kernels alone
+# ---------------------------------------------------------------------------------------------------------
+
+def _step(entries, ctx, slots):
+    """The device arrays of a step whose entries bring ``entries[i]`` tokens after ``ctx[i]`` cached ones."""
+    s = types.SimpleNamespace()
+    cu = np.concatenate([[0], np.cumsum(entries)]).astype(np.int32)
+    s.cu_q = torch.tensor(cu, device=dev())
+    s.ctx_len = torch.tensor(ctx, dtype=torch.int32, device=dev())
+    s.req_slot = torch.tensor(slots, dtype=torch.int32, device=dev())
+    s.token_req = torch.tensor(np.repeat(np.arange(len(entries)), entries), dtype=torch.int32, device=dev())
+    s.positions = torch.tensor(np.concatenate([np.arange(c, c + n) for n, c in zip(entries, ctx)]), dtype=torch.int32,
+                               device=dev())
+    s.num_entries = len(entries)
+    s.status = torch.zeros(1, dtype=torch.int32, device=dev())
+    return s
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("S,hidden", [(1, 100), (2, 64), (3, 90), (4, 37), (8, 24)])
+def test_streams_embedding_write_read_and_tanh_norm(dtype, S, hidden):
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(S)
+    T = 6
+    table = torch.randn(50, hidden, generator=g).to(torch.bfloat16)
+    ids = torch.tensor([3, 49, 0, 3, 7, 11], dtype=torch.int32, device=dev())
+    X = torch.empty(T, S * hidden, dtype=torch.float32, device=dev())
+    ops.embed_streams(X, table.to(dtype).to(dev()), ids, S, None)
+    assert torch.equal(X.cpu().view(T, S, hidden), table.float()[ids.cpu().long()][:, None, :].expand(T, S, hidden))
+    X = torch.randn(T, S * hidden, generator=g).to(dev())                 # streams that differ
+    alpha = torch.tensor([0.7], device=dev())
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(dev())
+    b = (0.1 * torch.randn(hidden, generator=g)).to(dev())
+    read = torch.randn(S, generator=g).to(dev())
+    mix = (torch.eye(S) + 0.3 * torch.randn(S, S, generator=g)).to(dev())
+    write = torch.randn(S, generator=g).to(dev())
+    y = torch.randn(T, hidden, generator=g).to(dtype).to(dev())
+    Xd = X.double().cpu().view(T, S, hidden).permute(1, 0, 2)
+
+    def ref(Xs, rd):
+        u = torch.einsum("i,itw->tw", rd, Xs)
+        return P.tanh_norm(u, alpha.double().cpu(), w.double().cpu(), b.double().cpu())
+
+    # read only (the first norm of a model; the last one reads the plain sum)
+    out = torch.empty(T, hidden, dtype=dtype, device=dev())
+    kept = X.clone()
+    ops.stream_tanh_norm(out, X, S, alpha, w, b, read)
+    assert torch.equal(X, kept)
+    assert rel_err(out.float().cpu().numpy(), ref(Xd, read.double().cpu()).numpy()) <= kernel_tol(dtype)
+    ops.stream_tanh_norm(out, X, S, alpha, w, b, None)
+    assert rel_err(out.float().cpu().numpy(), ref(Xd, torch.ones(S, dtype=P.F)).numpy()) <= kernel_tol(dtype)
+    # a pending write, all streams from the old ones (mix is indexed [from, to])
+    newX = torch.einsum("ij,itw->jtw", mix.double().cpu(), Xd) + write.double().cpu()[:, None, None] * y.double().cpu()[None]
+    X1 = X.clone()
+    ops.stream_tanh_norm(out, X1, S, alpha, w, b, read, y, mix, write)
+    assert torch.allclose(X1.double().cpu().view(T, S, hidden).permute(1, 0, 2), newX, atol=1e-5)
+    assert rel_err(out.float().cpu().numpy(), ref(newX, read.double().cpu()).numpy()) <= kernel_tol(dtype)
+    # the same with the output given as float32 partial sums of a split product
+    parts = torch.randn(3, T, hidden, generator=g).to(dev())
+    newXp = torch.einsum("ij,itw->jtw", mix.double().cpu(), Xd) + write.double().cpu()[:, None, None] * parts.double().cpu().sum(0)[None]
+    X2 = X.clone()
+    ops.stream_tanh_norm(out, X2, S, alpha, w, b, read, parts, mix, write)
+    assert torch.allclose(X2.double().cpu().view(T, S, hidden).permute(1, 0, 2), newXp, atol=1e-5)
+    # selected rows: nothing is written back
+    rows = torch.tensor([4, 0, 5], dtype=torch.int32, device=dev())
+    out3 = torch.empty(3, hidden, dtype=dtype, device=dev())
+    X3 = X.clone()
+    ops.stream_tanh_norm(out3, X3, S, alpha, w, b, None, y, mix, write, rows)
+    assert torch.equal(X3, X)
+    assert rel_err(out3.float().cpu().numpy(), ref(newX, torch.ones(S, dtype=P.F))[rows.cpu().long()].numpy()) <= kernel_tol(dtype)
+    assert torch.allclose(ops.stream_sum(X, S).double().cpu(), Xd.sum(0), atol=1e-5)
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,vd,rot,interleaved", [(3, 3, 24, 40, 10, True), (4, 2, 16, 8, 16, True),
+                                                          (2, 1, 20, 20, 0, True), (2, 2, 32, 48, 32, False)])
+def test_rotation_bias_and_cache_write(dtype, nh, nkv, hd, vd, rot, interleaved):
+    """Pairs (2i, 2i+1) on the first ``rot`` channels, scaled positions far beyond a few turns, biases, and the
+    write of keys and values of different widths into the pages the slot map names."""
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(hd)
+    T, ps, pages = 9, 4, 7
+    width = (nh + nkv) * hd + nkv * vd
+    qkv = torch.randn(T, width, generator=g).to(dtype)
+    bias = torch.randn(width, generator=g)
+    pos = torch.tensor([0, 1, 2, 3, 250, 4000, 70001, 5, 6], dtype=torch.int32)
+    base, factor = 500.0, 3.0
+    freq = None
+    if rot:
+        freq = (torch.tensor(base, dtype=torch.float64) ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)
+                / factor).float().to(dev())
+    slot_map = torch.tensor([5, 6, 7, 12, 0, 27, -1, 1, 2], dtype=torch.int32, device=dev())
+    kc = torch.full((pages, nkv, ps, hd), float("nan"), dtype=dtype, device=dev())
+    vc = torch.full((pages, nkv, ps, vd), float("nan"), dtype=dtype, device=dev())
+    x = qkv.to(dev()).clone()
+    ops.bias_rotate_store(x, bias.to(dev()), pos.to(dev()), freq, interleaved, nh, nkv, hd, vd, slot_map, kc, vc, ps, None)
+    full = qkv.double() + bias.double()
+    qk = full[:, :(nh + nkv) * hd].view(T, nh + nkv, hd)
+    if interleaved:
+        want_qk = P.rotate_pairs(qk, pos, rot, base, factor)
+    else:               # pairs (i, i + rot/2): the same turn on channels permuted to neighbours and back
+        perm = [c for i in range(rot // 2) for c in (i, i + rot // 2)] + list(range(rot, hd))
+        inv = np.argsort(perm)
+        want_qk = P.rotate_pairs(qk[..., perm], pos, rot, base, factor)[..., inv]
+    tol = 3e-5 if dtype == torch.float32 else 1.6e-2      # (float32 angles at position 70001: 1e-2 rad / 2^24 * 2^17)
+    got = x.double().cpu()
+    scale = float(full.abs().max())
+    assert float((got[:, :(nh + nkv) * hd].view(T, nh + nkv, hd) - want_qk).abs().max()) <= tol * scale * (40 if rot else 1)
+    assert float((got[:, (nh + nkv) * hd:] - full[:, (nh + nkv) * hd:]).abs().max()) <= tol * scale
+    for t in range(T):
+        s = int(slot_map[t])
+        if s < 0:
+            continue
+        assert torch.equal(kc[s // ps, :, s % ps, :].reshape(-1), x[t, nh * hd:(nh + nkv) * hd])
+        assert torch.equal(vc[s // ps, :, s % ps, :].reshape(-1), x[t, (nh + nkv) * hd:])
+    written = {int(s) for s in slot_map if s >= 0}
+    for s in range(pages * ps):
+        if s not in written:
+            assert bool(torch.isnan(kc[s // ps, :, s % ps]).all()) and bool(torch.isnan(vc[s // ps, :, s % ps]).all())
+
+
+def _paged(dtype, seqs_k, seqs_v, ps, nkv, hd, vd, rng):
+    """Keys/values of several requests scattered over a pool whose other slots hold NaN."""
+    n_pages = sum((len(k) + ps - 1) // ps for k in seqs_k) + 3
+    order = rng.permutation(n_pages)
+    kc = torch.full((n_pages, nkv, ps, hd), float("nan"), dtype=dtype)
+    vc = torch.full((n_pages, nkv, ps, vd), float("nan"), dtype=dtype)
+    max_blocks = max((len(k) + ps - 1) // ps for k in seqs_k)
+    bt = torch.full((len(seqs_k), max_blocks), -1, dtype=torch.int32)
+    at = 0
+    for r, (k, v) in enumerate(zip(seqs_k, seqs_v)):
+        for j in range(len(k)):
+            if j % ps == 0:
+                bt[r, j // ps] = int(order[at])
+                at += 1
+            kc[bt[r, j // ps], :, j % ps] = k[j].to(dtype)
+            vc[bt[r, j // ps], :, j % ps] = v[j].to(dtype)
+    return kc.to(dev()), vc.to(dev()), bt.to(dev())
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,vd,ps", [(3, 3, 24, 40, 4), (6, 2, 16, 8, 16), (9, 1, 20, 28, 8), (2, 1, 96, 300, 16)])
+def test_attention_with_values_wider_or_narrower_than_keys(dtype, nh, nkv, hd, vd, ps):
+    """Prompt portions and single tokens of three requests in one launch; in every request the query of the last
+    token is made to point at one far key (position 1, or the last of the first page), so that a key that is lost
+    or taken from a wrong page shows."""
+    from lite_lang_b200 import ops
+    rng = np.random.default_rng(hd)
+    g = torch.Generator().manual_seed(hd)
+    lens, new = [300, 47, 130], [20, 1, 1]
+    ks = [torch.randn(n, nkv, hd, generator=g) for n in lens]
+    vs = [torch.randn(n, nkv, vd, generator=g) for n in lens]
+    qs = [torch.randn(c, nh, hd, generator=g) for c in new]
+    far = [1, ps - 1, ps]
+    for r in range(3):
+        for h in range(nh):
+            qs[r][-1, h] = 25.0 * ks[r][far[r], h // (nh // nkv)] / ks[r][far[r], h // (nh // nkv)].norm()
+    ks = [k.to(dtype).float() for k in ks]
+    vs = [v.to(dtype).float() for v in vs]
+    qs = [q.to(dtype).float() for q in qs]
+    kc, vc, bt = _paged(dtype, ks, vs, ps, nkv, hd, vd, rng)
+    step = _step(new, [n - c for n, c in zip(lens, new)], [0, 1, 2])
+    q = torch.cat([x.reshape(x.shape[0], -1) for x in qs]).to(dtype).to(dev())
+    out = torch.empty(sum(new), nh * vd, dtype=dtype, device=dev())
+    scale = 0.37
+    ops.paged_attention_generic(out, q, q.stride(0), kc, vc, bt, step.token_req, step.req_slot, step.positions, sum(new),
+                                nh, nkv, hd, ps, None, scale, step.status, value_head_dim=vd)
+    assert int(step.status.item()) == 0
+    want = []
+    for r in range(3):
+        o = torch.stack([P.causal_softmax(torch.cat([torch.zeros(lens[r] - new[r], hd, dtype=P.F), qs[r][:, h].double()]),
+                                          ks[r][:, h // (nh // nkv)].double(), vs[r][:, h // (nh // nkv)].double(),
+                                          scale)[-new[r]:] for h in range(nh)], dim=1)
+        want.append(o.reshape(new[r], nh * vd))
+    want = torch.cat(want)
+    assert not bool(torch.isnan(out).any())
+    assert rel_err(out.float().cpu().numpy(), want.numpy()) <= kernel_tol(dtype)
+    # the far key dominates the last rows: their output is close to that key's value
+    last = out[new[0] - 1].float().cpu().view(nh, vd)
+    assert float((last[0] - vs[0][far[0], 0]).abs().max()) < 0.5 * float(vs[0][far[0], 0].abs().max())
+
+
+def _scan_reference(proj, off, H, dk, dv, decay):
+    q = P.silu(proj[:, off[0]:off[0] + H * dk]).view(-1, H, dk)
+    k = P.silu(proj[:, off[1]:off[1] + H * dk]).view(-1, H, dk)
+    v = P.silu(proj[:, off[2]:off[2] + H * dv]).view(-1, H, dv)
+    o = torch.stack([P.decay_recurrence(q[:, h], k[:, h], v[:, h], decay[h])[0] for h in range(H)], dim=1)
+    return o.reshape(-1, H * dv)
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,dk,dv", [(3, 20, 12), (1, 40, 36), (2, 128, 64), (5, 16, 16), (2, 24, 44), (1, 200, 17)])
+def test_decay_scan_in_portions_side_by_side_and_in_slots_used_again(dtype, H, dk, dv):
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(dk)
+    decay = [0.3, 0.999, 1.0, 0.9, 0.6][:H]
+    off = (8, 8 + H * dk + 3, 8 + 2 * H * dk + 11)
+    width = off[2] + H * dv + 5
+    lens = [70, 33, 1]
+    projs = [torch.randn(n, width, generator=g).to(dtype).float() for n in lens]
+    refs = [_scan_reference(p.double(), off, H, dk, dv, decay) for p in projs]
+    dec = torch.tensor(decay, device=dev())
+    state = torch.full((4, H * dv * dk), float("nan"), device=dev())
+    state[[3, 1, 0]] = 0.0                                       # slots as the storage leaves them when opened
+    slots = [3, 1, 0]
+    cuts = [[17, 2, 16, 1, 31, 2, 1], [2, 1, 30], [1]]          # portions down to two tokens, and single tokens
+    at, got = [0, 0, 0], [[], [], []]
+    while any(at[r] < lens[r] for r in range(3)):
+        live = [r for r in range(3) if at[r] < lens[r]]
+        counts = [cuts[r].pop(0) for r in live]
+        x = torch.cat([projs[r][at[r]:at[r] + c] for r, c in zip(live, counts)]).to(dtype).to(dev())
+        step = _step(counts, [at[r] for r in live], [slots[r] for r in live])
+        o = torch.empty(x.shape[0], H * dv, device=dev())
+        ops.decay_scan(x, off[0], off[1], off[2], dec, state, step, o, H, dk, dv)
+        t = 0
+        for r, c in zip(live, counts):
+            got[r].append(o[t:t + c].double().cpu())
+            t, at[r] = t + c, at[r] + c
+    for r in range(3):
+        assert rel_err(torch.cat(got[r]).numpy(), refs[r].numpy()) <= 1e-4, r
+    assert bool(torch.isnan(state[2]).all())                     # a slot nobody owns is not touched
+    # a slot used again: zeroed, it gives the whole-prompt result in one go; a padding entry writes zeros
+    state[1] = 0.0
+    x = torch.cat([projs[0], projs[2]]).to(dtype).to(dev())
+    step = _step([lens[0], 1], [0, 0], [1, -1])
+    o = torch.full((x.shape[0], H * dv), float("nan"), device=dev())
+    ops.decay_scan(x, off[0], off[1], off[2], dec, state, step, o, H, dk, dv)
+    assert rel_err(o[:lens[0]].double().cpu().numpy(), refs[0].numpy()) <= 1e-4
+    assert bool((o[lens[0]:] == 0).all())
+    # not writable: the record stays as it is
+    kept = state.clone()
+    ops.decay_scan(x, off[0], off[1], off[2], dec, state, _step([lens[0], 1], [0, 0], [3, -1]), o, H, dk, dv, False)
+    assert torch.equal(torch.nan_to_num(state), torch.nan_to_num(kept))
+
+
+@gpu
+def test_decay_scan_keeps_a_far_write_and_forgets_with_a_small_decay():
+    """One token early in a long prompt writes a large k v^T; a query for it hundreds of tokens later reads it back
+    times decay^distance: kept by a decay near 1, gone with a small one."""
+    from lite_lang_b200 import ops
+    H, dk, dv, T = 2, 32, 16, 600
+    proj = torch.full((T, H * (2 * dk + dv)), -200.0)             # silu(-200) is 0 in float32: silent tokens
+    ko, vo = H * dk, 2 * H * dk
+    for h in range(H):
+        proj[5, ko + h * dk + 3] = 10.0                          # k_5 = 10 e_3
+        proj[5, vo + h * dv:vo + (h + 1) * dv] = torch.arange(1, dv + 1).float()
+        proj[T - 1, h * dk + 3] = 2.0                            # q_last = silu(2) e_3
+    decay = [0.9995, 0.5]
+    state = torch.zeros(1, H * dv * dk, device=dev())
+    o = torch.empty(T, H * dv, device=dev())
+    for lo, hi in ((0, 4), (4, 6), (6, 333), (333, T - 1), (T - 1, T)):     # cuts right before and after the write
+        ops.decay_scan(proj[lo:hi].to(dev()), 0, ko, vo, torch.tensor(decay, device=dev()), state,
+                       _step([hi - lo], [lo], [0]), o[lo:hi], H, dk, dv)
+    silu = lambda z: z / (1 + np.exp(-z))
+    v5 = silu(np.arange(1, dv + 1, dtype=np.float64))
+    want0 = decay[0] ** (T - 1 - 5) * silu(2.0) * silu(10.0) * v5
+    assert np.allclose(o[T - 1, :dv].double().cpu().numpy(), want0, rtol=2e-4)
+    assert float(o[T - 1, dv:].abs().max()) < 1e-30
+    assert np.allclose(o[5, :dv].cpu().numpy(), 0.0) and float(o[:5].abs().max()) == 0.0
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_linear_attention_output_norm_gate_and_the_join_of_two_mixers(dtype):
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(2)
+    T, width = 7, 90
+    o = torch.randn(T, width, generator=g) * 30
+    w = 1 + 0.1 * torch.randn(width, generator=g)
+    gate = torch.randn(T, width + 6, generator=g).to(dtype)
+    y = torch.empty(T, width, dtype=dtype, device=dev())
+    ops.linear_attn_out(y, o.to(dev()), w.to(dev()), gate.to(dev())[:, 3:3 + width], 1e-5)
+    want = P.rms_norm(o.double(), w.double(), 1e-5) * P.sigmoid(gate.double()[:, 3:3 + width])
+    assert rel_err(y.float().cpu().numpy(), want.numpy()) <= kernel_tol(dtype)
+    a = (torch.randn(T, width, generator=g) * 4).to(dtype)
+    b = (torch.randn(T, width, generator=g) * 0.01).to(dtype)       # two outputs of very different size
+    ba, wa, wb = torch.randn(width, generator=g), torch.randn(width, generator=g), torch.randn(width, generator=g)
+    out = torch.empty(T, width, dtype=dtype, device=dev())
+    ops.rms_pair_mean(out, a.to(dev()), ba.to(dev()), wa.to(dev()), b.to(dev()), wb.to(dev()), 3e-6)
+    want = 0.5 * (P.rms_norm(a.double() + ba.double(), wa.double(), 3e-6) + P.rms_norm(b.double(), wb.double(), 3e-6))
+    assert rel_err(out.float().cpu().numpy(), want.numpy()) <= kernel_tol(dtype)
+    ops.rms_pair_mean(out, a.to(dev()), None, wa.to(dev()), b.to(dev()), wb.to(dev()), 3e-6)
+    want = 0.5 * (P.rms_norm(a.double(), wa.double(), 3e-6) + P.rms_norm(b.double(), wb.double(), 3e-6))
+    assert rel_err(out.float().cpu().numpy(), want.numpy()) <= kernel_tol(dtype)
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_small_elementwise_kernels(dtype):
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    gu = torch.randn(5, 2 * 33, generator=g).to(dtype)
+    out = torch.empty(5, 33, dtype=dtype, device=dev())
+    ops.act_mul(out, gu.to(dev()), "relu")
+    want = torch.relu(gu.double()[:, :33]) * gu.double()[:, 33:]
+    assert rel_err(out.float().cpu().numpy(), want.numpy()) <= kernel_tol(dtype)
+    ops.act_mul(out, gu.to(dev()), "silu")
+    assert rel_err(out.float().cpu().numpy(), (P.silu(gu.double()[:, :33]) * gu.double()[:, 33:]).numpy()) <= kernel_tol(dtype)
+    x = torch.randn(4, 21, generator=g).to(dtype)
+    bias = torch.randn(21, generator=g)
+    xd = x.to(dev()).clone()
+    ops.add_bias(xd, bias.to(dev()))
+    assert rel_err(xd.float().cpu().numpy(), (x.double() + bias.double()).numpy()) <= kernel_tol(dtype)
+    z = (torch.randn(3, 50, generator=g) * 40).to(dev())
+    want = 12.0 * torch.tanh(z.double().cpu() / 12.0)
+    ops.softcap(z, 12.0)
+    assert torch.allclose(z.double().cpu(), want, atol=1e-5) and float(z.abs().max()) <= 12.0
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("E,top,ff,shared,tokens", [(4, 4, 24, 0, 9), (12, 1, 24, 48, 40), (5, 2, 20, 12, 150),
+                                                   (8, 3, 16, 8, 200)])
+def test_routed_gated_experts_part(dtype, E, top, ff, shared, tokens):
+    """The part against the plain formulas, by the stacked way (few tokens, float32) and the grouped way (many
+    tokens, bfloat16): chosen experts, softmax over the chosen logits only, router bias, clamps on both sides of
+    the limit, the shared expert with a limit of its own and its sigmoid gate."""
+    from lite_lang_b200.config.spec import PartSpec
+    from lite_lang_b200.parts import build_part
+    hidden = 64
+    spec = PartSpec("routed_experts", {"hidden_size": hidden, "experts": E, "top": top, "expert_ff": ff,
+                                       "shared_ff": shared, "gated": True, "limit": 0.8, "shared_limit": 0.3,
+                                       "score": "softmax_top", "router_bias": True, "shared_gate": shared > 0}, "m.")
+    part = build_part("feed_forward", spec)
+    g = torch.Generator().manual_seed(E)
+    w = {}
+    for name, decl in part.tensors().items():
+        std = 2.0 if name.startswith("router") else 0.25
+        w["m." + name] = (std * torch.randn(tuple(decl.shape), generator=g)).to(torch.bfloat16)
+    part.load(lambda rel: w["m." + rel], dtype, dev())
+    x = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16)
+    wd = {k: v.double() for k, v in w.items()}
+    mlp = {"router": {"top": top}, "expert": {"limit": 0.8}, "shared": {"limit": 0.3} if shared else None}
+    want = P.moe_ff(x.double(), wd, "m.", mlp)
+    step = types.SimpleNamespace(captured=False)
+    got = part.forward(x.to(dtype).to(dev()), step)
+    if got.dim() == 3:
+        got = got.sum(0)
+    e = row_errors(got.float().cpu().numpy(), want.numpy())
+    # the clamps are active on a good part of the units, so a limit that is left out or one-sided would show
+    gates = x.double() @ wd["m.e0.gate"].T
+    assert float((gates > 0.8).double().mean()) > 0.05 and float((gates < -0.8).double().mean()) > 0.05
+    if dtype == torch.float32:
+        assert e.max() <= 2e-5
+    else:
+        assert int((e > 3e-2).sum()) <= max(1, tokens // 20)      # (a near-tie of the router in bfloat16)
+    idx, wts = P.route(x.double(), wd, "m.", top)
+    gates_k, top_idx, top_w = part.route(x.to(dtype).to(dev()))
+    assert torch.equal(torch.sort(top_idx.cpu().long(), dim=1).values, torch.sort(idx, dim=1).values)
+    assert torch.allclose(top_w.double().cpu().sum(1), torch.ones(tokens, dtype=P.F), atol=1e-5)
+    assert torch.allclose(top_w.double().cpu(), wts, atol=1e-4)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# GPU: whole models through the step function and the cache manager
+# ---------------------------------------------------------------------------------------------------------
+
+_FOLDERS = {}
+
+
+def _case(name):
+    if name not in _FOLDERS:
+        folder = write_folder(name, sharpen=3.0)
+        cfg, w = P.read_model_folder(folder)
+        rng = np.random.default_rng(CASES[name]["seed"])
+        seqs = [[int(t) for t in rng.integers(0, cfg["vocab"], n)] for n in (150, 61, 97, 1, 34, 120)]
+        refs = [P.forward(cfg, w, s).numpy() for s in seqs]
+        _FOLDERS[name] = (folder, seqs, refs)
+    return _FOLDERS[name]
+
+
+def _runner(folder, dtype, page_size, num_pages, slots=4, graphs=True, max_len=256):
+    from lite_lang_b200.cache.manager import CacheManager
+    from lite_lang_b200.config.base import load_config
+    from lite_lang_b200.engine.model import CausalLM
+    from lite_lang_b200.engine.runner import ModelRunner
+    from lite_lang_b200.weights.loader import load_weights
+    model = CausalLM(load_config(folder).model_spec())
+    load_weights(model, folder, dtype, dev())
+    n_paged = sum(1 for g in model.cache_groups if g.kind == "paged")
+    mgr = CacheManager(model.cache_groups, [num_pages] * n_paged, page_size, slots, max_len)
+    return mgr, ModelRunner(model, mgr, dev(), 512, cuda_graphs=graphs)
+
+
+def _feed(runner, mgr, slot, toks, want=None):
+    from lite_lang_b200.engine.batch import StepEntry
+    assert runner.reserve(slot, len(toks))
+    want = tuple(range(len(toks))) if want is None else want
+    return runner.step([StepEntry(slot, toks, want)]).float().cpu().numpy().copy()
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["P", "Q", "R"])
+def test_whole_decode_and_portions(name, dtype):
+    folder, seqs, refs = _case(name)
+    mgr, runner = _runner(folder, dtype, CASES[name]["page_size"], 256 // CASES[name]["page_size"])
+    for i in (0, 3, 4):                                     # whole prompts (one of them a single token)
+        s = mgr.open()
+        assert close(_feed(runner, mgr, s, seqs[i]), refs[i], dtype), f"{name} whole {i}"
+        mgr.close(s)
+    for i in (0, 2):                                        # a prompt, then 40 tokens one by one (captured steps)
+        s, n = mgr.open(), len(seqs[i])
+        head = n - 40
+        got = [_feed(runner, mgr, s, seqs[i][:head])] + [_feed(runner, mgr, s, seqs[i][t:t + 1]) for t in range(head, n)]
+        assert close(np.concatenate(got), refs[i], dtype), f"{name} decode {i}"
+        mgr.close(s)
+    s, n = mgr.open(), len(seqs[1])                         # from the very first token on, one by one
+    got = [_feed(runner, mgr, s, seqs[1][t:t + 1]) for t in range(n)]
+    assert close(np.concatenate(got), refs[1], dtype), f"{name} token by token"
+    mgr.close(s)
+    sizes = [7, 2, 13, 2, 5, 31, 2, 3, 17, 2, 64, 2, 9]
+    for i in (0, 5):                                        # portions of changing size, down to two tokens
+        s, n, t, k, got = mgr.open(), len(seqs[i]), 0, 0, []
+        while t < n:
+            c = min(sizes[k % len(sizes)], n - t)
+            got.append(_feed(runner, mgr, s, seqs[i][t:t + c]))
+            t, k = t + c, k + 1
+        assert close(np.concatenate(got), refs[i], dtype), f"{name} portions {i}"
+        mgr.close(s)
+    runner.check_status()
+    assert runner.graph_replays > 0
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["P", "Q", "R"])
+def test_mixed_batches_with_pages_and_slots_used_again(name, dtype, monkeypatch):
+    from lite_lang_b200.engine.batch import StepEntry
+    monkeypatch.setenv("LITE_LANG_B200_CACHE_FILL", "nan")
+    folder, seqs, refs = _case(name)
+    ps = CASES[name]["page_size"]
+    order = [0, 1, 2, 3, 4, 5, 1, 2, 0]
+    need = sorted(((len(seqs[i]) + ps - 1) // ps for i in order), reverse=True)[:3]
+    mgr, runner = _runner(folder, dtype, ps, sum(need) + 1, slots=3)
+    rng = np.random.default_rng(3)
+    waiting, live, all_got, all_ref = list(enumerate(order)), {}, [], []
+    while waiting or live:
+        while waiting and len(live) < 3:
+            k, i = waiting.pop(0)
+            live[k] = [i, 0, mgr.open()]
+        entries, expect, done = [], [], []
+        for k, (i, t, slot) in list(live.items()):
+            n = len(seqs[i])
+            if len(live) > 1 and rng.random() < 0.2:
+                continue                                    # left out of this step, goes on later
+            c = min(int(rng.integers(2, 23)) if n - t > 20 else 1, n - t)
+            assert runner.reserve(slot, c)
+            want = tuple(range(c)) if rng.random() < 0.7 else (c - 1,)
+            entries.append(StepEntry(slot, seqs[i][t:t + c], want))
+            expect.append(refs[i][[t + w for w in want]])
+            live[k][1] = t + c
+            if t + c == n:
+                done.append(k)
+        if not entries:
+            continue
+        got = runner.step(entries).float().cpu().numpy()
+        all_got.append(got.copy())
+        all_ref.append(np.concatenate(expect))
+        for k in done:
+            mgr.close(live.pop(k)[2])
+        mgr.check_invariants()
+    runner.check_status()
+    assert close(np.concatenate(all_got), np.concatenate(all_ref), dtype), name
+    assert mgr.pages_reused > 0
+
+
+@gpu
+def test_replay_tool_and_a_prompt_of_many_tokens_in_one_step():
+    """The command-line replay on a folder: a prompt long enough for the grouped experts and the prompt attention
+    kernels, cut into three steps beside a short request that ends early."""
+    folder = write_folder("Q", sharpen=3.0)
+    cfg, w = P.read_model_folder(folder)
+    toks = [int(t) for t in np.random.default_rng(9).integers(0, cfg["vocab"], 260)]
+    ref = P.forward(cfg, w, toks).numpy()
+    for dtype in ("float32", "bfloat16"):
+        tr = TraceRun(folder, dtype, max_tokens=384, page_size=16)
+        try:
+            a = tr.step([{"id": "a", "tokens": toks[:200], "want": list(range(0, 200, 7))}])
+            b = tr.step([{"id": "a", "tokens": toks[200:259], "want": list(range(59))},
+                         {"id": "b", "tokens": toks[:5], "want": [4]}], end=["b"])
+            c = tr.step([{"id": "a", "tokens": toks[259:], "want": [0]}], end=["a"])
+        finally:
+            assert tr.close() == 0
+        want = np.concatenate([ref[0:200:7], ref[200:259], ref[259:], ref[4:5]])
+        assert close(np.concatenate([a, b[:59], c, b[59:]]), want, dtype)
+
+
+@gpu
+def test_greedy_generation_through_the_scheduler():
+    """Engine.generate with more prompts than request slots: the tokens are the plain implementation's greedy
+    continuation (float32, so that no near-tie decides)."""
+    from lite_lang_b200 import Engine, EngineConfig, SamplingParams
+    folder = write_folder("R", sharpen=3.0)
+    cfg, w = P.read_model_folder(folder)
+    rng = np.random.default_rng(4)
+    prompts = [[int(t) for t in rng.integers(0, cfg["vocab"], n)] for n in (9, 30, 1, 17, 44)]
+    new = 12
+    engine = Engine(folder, EngineConfig(dtype="float32", page_size=8, num_pages=40, max_batch_size=3,
+                                         max_input_length=64, max_output_length=new, max_tokens_per_step=48))
+    outs = engine.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=new, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        seq = list(p)
+        for k in range(new):
+            logits = P.forward(cfg, w, seq)[-1]
+            top2 = torch.topk(logits, 2).values
+            if float(top2[0] - top2[1]) < 1e-3:          # a near-tie: either token is right, stop comparing
+                break
+            assert int(torch.argmax(logits)) == o[k], (len(p), k)
+            seq.append(o[k])
+    st = engine.stats()
+    assert st["graph_replays"] > 0
