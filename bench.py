@@ -476,6 +476,27 @@ def _nevurax_shape(width, heads, kv_heads, head, inter, vocab, layers, window, e
             "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": moe} for i in range(layers)]}
 
 
+def _redirax_shape(width, heads, kv_heads, head, inter, vocab, layers, window, experts, top):
+    """A Redirax model whose layers are as large as a Qwen2 layer of the given sizes: the softmax attention has the
+    same heads (values as wide as keys), the linear attention beside it as many heads of the same size; the first
+    layer's feed-forward is the dense gated one, the others route ``top`` of ``experts`` gated experts (+ a shared
+    one) with as many *active* weights as the dense one; two residual streams."""
+    ff = inter // (top + 1) // 64 * 64
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff, "limit": 7.0},
+           "shared": {"ff": ff, "limit": 7.0}}
+    dense = {"kind": "dense", "ff": inter}
+    mixer = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5,
+                      "rot": {"base": 1e6, "dims": head, "scaling": {"factor": 4.0}}},
+             "right": {"heads": heads, "dim": head, "vdim": head,
+                       "decay": [1.0 - 2.0 ** (-2 - 6 * h / max(heads - 1, 1)) for h in range(heads)]}}
+    return {"architecture": "Redirax", "vocab": vocab, "width": width, "streams": 2, "norm": {"eps": 1e-6},
+            "logit_softcap": 30.0,
+            "layers": [{"type": "parallel", "mixer": mixer, "mlp": dense if i % 4 == 0 else moe}
+                       for i in range(layers)]}
+
+
+COMPARE_DESIGNS = {"nevurax": _nevurax_shape, "redirax": _redirax_shape}
+
 COMPARE_SIZES = {
     # name: (Qwen2 sizes, window of the latent attention, experts, top)
     "1p5b": (dict(QWEN2_1P5B, vocab_size=32768), 512, 16, 4),
@@ -509,19 +530,25 @@ def _kernel_table(engine, entries_fn, steps=3):
 
 def run_compare(args):
     """Prefill (2,048 tokens) and decode (batch 8 and 64 at context 2,048) of a few layers of both designs."""
+    # (a Nevurax arm needs its last layer to have a feed-forward for the configuration note; all of them have)
     import torch
     from lite_lang_b200.engine.batch import StepEntry
     pk = peaks()
     layers = args.layers or 4
-    out = {"compare": "nevurax", "layers": layers, "dtype": "bfloat16", "data": "synthetic", "peaks": pk, "sizes": {}}
+    design_name = args.compare
+    out = {"compare": design_name, "layers": layers, "dtype": "bfloat16", "data": "synthetic", "peaks": pk, "sizes": {}}
     for name, (qwen, window, experts, top) in COMPARE_SIZES.items():
         if args.shape_name and args.shape_name != name:
             continue
         row = {}
-        nev = _nevurax_shape(qwen["hidden_size"], qwen["num_attention_heads"], qwen["num_key_value_heads"],
-                             qwen["hidden_size"] // qwen["num_attention_heads"], qwen["intermediate_size"],
-                             qwen["vocab_size"], layers, window, experts, top)
-        for design, model in (("qwen2", qwen), ("nevurax", nev)):
+        nev = COMPARE_DESIGNS[design_name](
+            qwen["hidden_size"], qwen["num_attention_heads"], qwen["num_key_value_heads"],
+            qwen["hidden_size"] // qwen["num_attention_heads"], qwen["intermediate_size"], qwen["vocab_size"], layers,
+            window, experts, top)
+        designs = (("qwen2", qwen), (design_name, nev))
+        if args.design_only:
+            designs = designs[1:]
+        for design, model in designs:
             engine = build_engine(layers, 64, model=model)
             r = {"weight_bytes": engine.model.weight_bytes_per_step()}
             pre = prefill_once(engine, repeats=10, seconds=0.3)
@@ -558,8 +585,8 @@ def run_compare(args):
             row[design] = r
             del engine
             torch.cuda.empty_cache()
-        row["config"] = {"nevurax": {"window": window, "experts": experts, "top": top,
-                                     "expert_ff": nev["layers"][0]["mlp"]["expert"]["ff"]}}
+        row["config"] = {design_name: {"window": window if design_name == "nevurax" else None, "experts": experts,
+                                       "top": top, "expert_ff": nev["layers"][-1]["mlp"]["expert"]["ff"]}}
         out["sizes"][name] = row
     print(json.dumps(out))
     return 0
@@ -667,7 +694,9 @@ def main():
                     help="with --only decode: another context length than the headline's 2,048 prompt tokens")
     ap.add_argument("--shape", default="", choices=[""] + sorted(WORKLOADS),
                     help="with --only: the layer sizes of that workload's model instead of Qwen2-1.5B's")
-    ap.add_argument("--compare", default="", choices=["", "nevurax"],
+    ap.add_argument("--design-only", action="store_true", dest="design_only",
+                    help="with --compare: leave the Qwen2 arm out")
+    ap.add_argument("--compare", default="", choices=["", "nevurax", "redirax"],
                     help="instead of the headline measurement: prefill and decode of a few layers of that design beside "
                          "Qwen2 at equal layer sizes (random weights); --layers (default 4), --size, --kernels go with it")
     ap.add_argument("--size", default="", dest="shape_name", choices=[""] + sorted(COMPARE_SIZES),

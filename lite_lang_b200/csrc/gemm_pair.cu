@@ -173,6 +173,7 @@ struct GpParams {
   int m_tiles;      // tiles of 256 tokens
   int tiles;        // m_tiles x column tiles (plain: 256 features a tile, gated: 128)
   int vec_ok;       // the output takes 16-byte pieces (aligned base and stride, N a multiple of 8)
+  int act;          // gated: 0 silu(gate) * up, 1 relu(gate) * up
   int* status;
   // q|k|v mode only: what follows the projection (N = (nh + 2 nkv) hd; out is q [M, nh hd])
   const float* bias;      // float32 [N] or null
@@ -506,7 +507,7 @@ gemm_pair_kernel(const GpParams p, const __grid_constant__ CUtensorMap wmap, con
               const float uv = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[i])));
               // (x * rcp(y) instead of the IEEE division: that one's chain of dependent instructions with a
               //  branch an element, on the one warp a scheduler has here, made the epilogue twice as long as the MMAs)
-              v[i] = __fdividef(gt, 1.0f + __expf(-gt)) * uv;
+              v[i] = p.act ? fmaxf(gt, 0.f) * uv : __fdividef(gt, 1.0f + __expf(-gt)) * uv;
             }
           } else {
             unsigned a[32];
@@ -640,6 +641,7 @@ extern "C" int ll_gemm_pair(void* out, long out_stride, const void* x, long x_st
   p.N = N;
   p.K = K;
   p.status = status;
+  p.act = gated == 2 ? 1 : 0;      // (gated: 1 SiLU, 2 ReLU)
   p.vec_ok = ((uintptr_t)out % 16 == 0 && out_stride % 8 == 0 && N % 8 == 0) ? 1 : 0;
   p.bias = nullptr;
   p.positions = nullptr;
@@ -674,6 +676,7 @@ extern "C" int ll_gemm_pair_qkv_rope(void* q_out, long q_stride, const void* x, 
   p.N = (nh + 2 * nkv) * hd;
   p.K = K;
   p.status = status;
+  p.act = 0;
   p.vec_ok = 1;
   p.bias = bias;
   p.positions = positions;

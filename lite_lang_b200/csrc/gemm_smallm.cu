@@ -50,8 +50,8 @@ template <> __device__ __forceinline__ bf16 gs_out<bf16>(float v) { return __flo
 template <int MT, bool GATED, typename OutT>
 __global__ void __launch_bounds__(GS_THREADS)
 gemm_smallm_kernel(OutT* __restrict__ out, long out_stride, const bf16* __restrict__ x, long x_stride,
-                   const bf16* __restrict__ w, int M, int N, int K) {
-  // N is the number of output features (for GATED: the intermediate size I; W has 2 I rows)
+                   const bf16* __restrict__ w, int M, int N, int K, int act) {
+  // N is the number of output features (act: the gate's activation, 0 SiLU, 1 ReLU) (for GATED: the intermediate size I; W has 2 I rows)
   extern __shared__ float red[];  // [GS_WARPS][GATED ? 2 : 1][16][8 * MT]
   constexpr int TOK = 8 * MT;
   constexpr int NACC = GATED ? 2 : 1;
@@ -149,7 +149,7 @@ gemm_smallm_kernel(OutT* __restrict__ out, long out_stride, const bf16* __restri
       // rounded to the storage type first, as the unfused path does between the product and the activation
       const float gt = __bfloat162float(__float2bfloat16_rn(v[0]));
       const float up = __bfloat162float(__float2bfloat16_rn(v[NACC - 1]));
-      y = gt / (1.0f + expf(-gt)) * up;
+      y = (act ? fmaxf(gt, 0.f) : gt / (1.0f + expf(-gt))) * up;
     }
     out[(size_t)tok * out_stride + f0 + f] = gs_out<OutT>(y);
   }
@@ -157,22 +157,22 @@ gemm_smallm_kernel(OutT* __restrict__ out, long out_stride, const bf16* __restri
 
 template <int MT, bool GATED, typename OutT>
 static int gs_launch(void* out, long out_stride, const void* x, long x_stride, const void* w, int M, int N, int K,
-                     cudaStream_t stream) {
+                     int act, cudaStream_t stream) {
   const size_t smem = sizeof(float) * GS_WARPS * (GATED ? 2 : 1) * 16 * 8 * MT;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(gemm_smallm_kernel<MT, GATED, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   ll_launch(gemm_smallm_kernel<MT, GATED, OutT>, dim3((N + 15) / 16), dim3(GS_THREADS), smem, stream, (OutT*)out,
-            out_stride, (const bf16*)x, x_stride, (const bf16*)w, M, N, K);
+            out_stride, (const bf16*)x, x_stride, (const bf16*)w, M, N, K, act);
   return LL_LAUNCH_RESULT();
 }
 
 template <bool GATED, typename OutT>
 static int gs_dispatch_m(void* out, long out_stride, const void* x, long x_stride, const void* w, int M, int N, int K,
-                         cudaStream_t stream) {
-  if (M <= 8) return gs_launch<1, GATED, OutT>(out, out_stride, x, x_stride, w, M, N, K, stream);
-  if (M <= 16) return gs_launch<2, GATED, OutT>(out, out_stride, x, x_stride, w, M, N, K, stream);
-  if (M <= 32) return gs_launch<4, GATED, OutT>(out, out_stride, x, x_stride, w, M, N, K, stream);
-  if (M <= 64) return gs_launch<8, GATED, OutT>(out, out_stride, x, x_stride, w, M, N, K, stream);
+                         int act, cudaStream_t stream) {
+  if (M <= 8) return gs_launch<1, GATED, OutT>(out, out_stride, x, x_stride, w, M, N, K, act, stream);
+  if (M <= 16) return gs_launch<2, GATED, OutT>(out, out_stride, x, x_stride, w, M, N, K, act, stream);
+  if (M <= 32) return gs_launch<4, GATED, OutT>(out, out_stride, x, x_stride, w, M, N, K, act, stream);
+  if (M <= 64) return gs_launch<8, GATED, OutT>(out, out_stride, x, x_stride, w, M, N, K, act, stream);
   return (int)cudaErrorInvalidValue;
 }
 
@@ -182,10 +182,11 @@ extern "C" int ll_gemm_smallm(void* out, long out_stride, int out_f32, const voi
                               int M, int N, int K, int gated, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64 || K <= 0 || (K % 32) != 0 || (x_stride % 8) != 0) return (int)cudaErrorInvalidValue;
+  const int act = gated == 2 ? 1 : 0;      // (gated: 1 SiLU, 2 ReLU)
   if (gated) {
     if (out_f32) return (int)cudaErrorInvalidValue;
-    return gs_dispatch_m<true, bf16>(out, out_stride, x, x_stride, w, M, N, K, stream);
+    return gs_dispatch_m<true, bf16>(out, out_stride, x, x_stride, w, M, N, K, act, stream);
   }
-  if (out_f32) return gs_dispatch_m<false, float>(out, out_stride, x, x_stride, w, M, N, K, stream);
-  return gs_dispatch_m<false, bf16>(out, out_stride, x, x_stride, w, M, N, K, stream);
+  if (out_f32) return gs_dispatch_m<false, float>(out, out_stride, x, x_stride, w, M, N, K, act, stream);
+  return gs_dispatch_m<false, bf16>(out, out_stride, x, x_stride, w, M, N, K, act, stream);
 }

@@ -143,6 +143,7 @@ struct GtParams {
   int units;    // feature units times ksplit
   int ksplit;   // parts the k range is cut into; > 1: out is float32 [ksplit, M, N] partial sums
   int cpp;      // k chunks (stages) per part
+  int act;      // GATED: 0 silu(gate) * up, 1 relu(gate) * up
   // QKV_ROPE only: what follows the projection
   const float* bias;       // float32 [(nh + 2 nkv) hd] or null
   const int* positions;    // int32 [M]
@@ -471,7 +472,7 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
               const float rs = SPLIT ? row_scale[t] : 1.0f;
               const float gt = __bfloat162float(__float2bfloat16_rn(acc[j][h] * rs));
               const float up = __bfloat162float(__float2bfloat16_rn(acc[j][2 + h] * rs));
-              out[(size_t)t * p.out_stride + f] = gt_out<OutT>(gt / (1.0f + expf(-gt)) * up);
+              out[(size_t)t * p.out_stride + f] = gt_out<OutT>((p.act ? fmaxf(gt, 0.f) : gt / (1.0f + expf(-gt))) * up);
             }
           }
         }
@@ -657,6 +658,8 @@ extern "C" int ll_gemm_stream(void* out, long out_stride, int out_f32, const voi
                               int M, int N, int K, int mode, int ksplit, int sm_count, int* status,
                               cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
+  const int act = mode >> 8;      // (bits from 8 on: the gated mode's activation, 0 SiLU, 1 ReLU)
+  mode &= 0xff;
   if (M > 64 || K <= 0 || (x_stride % 8) != 0 || sm_count <= 0 || ksplit < 1) return (int)cudaErrorInvalidValue;
   // (33 to 64 tokens: units of 16 features to bfloat16 only, in two blocks of tokens)
   if (M > 32 && (mode != GT_MODE_NARROW || out_f32 || ksplit != 1)) return (int)cudaErrorInvalidValue;
@@ -669,6 +672,7 @@ extern "C" int ll_gemm_stream(void* out, long out_stride, int out_f32, const voi
   p.M = M;
   p.N = N;
   p.K = K;
+  p.act = act == 1 ? 1 : 0;
   p.status = status;
   if (mode == GT_MODE_WIDE) {
     if (K % 128) return (int)cudaErrorInvalidValue;

@@ -102,6 +102,7 @@ struct TcParams {
   int ksplit;    // > 1: out is float32 [ksplit, M, N] partial sums
   int cpp;       // 64-wide k boxes per part
   int vec_ok;    // the output takes 16-byte pieces (aligned base and stride, N a multiple of the piece)
+  int act;       // gated: 0 silu(gate) * up, 1 relu(gate) * up
   // SCALED (gated, at most 64 tokens): the tokens' rows are only multiplied by the weight of the norm before this
   // product yet; the rows' sums of squares come in parts [sumsq_units][64] (see gemm_stream.cu: the product before
   // the norm leaves them), and each row of the result is scaled by 1 / sqrt(sum / K + eps) before the activation
@@ -326,7 +327,7 @@ gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap wmap, const
           const float gt = __bfloat162float(__float2bfloat16_rn(a * rs));
           const float uv = __bfloat162float(__float2bfloat16_rn(stg[(64 + fl) * (NT + 1) + t] * rs));
           // (x * rcp(y), not the IEEE division: that is a chain of dependent instructions with a branch an element)
-          return __fdividef(gt, 1.0f + __expf(-gt)) * uv;
+          return p.act ? fmaxf(gt, 0.f) * uv : __fdividef(gt, 1.0f + __expf(-gt)) * uv;
         }
         return a;
       };
@@ -441,6 +442,7 @@ extern "C" int ll_gemm_tc(void* out, long out_stride, int out_f32, const void* x
   p.N = N;
   p.K = K;
   p.status = status;
+  p.act = gated == 2 ? 1 : 0;      // (gated: 1 SiLU, 2 ReLU)
   p.sumsq_in = sumsq;
   p.sumsq_units = sumsq_units;
   p.norm_eps = norm_eps;

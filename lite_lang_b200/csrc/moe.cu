@@ -17,39 +17,47 @@
 // [tokens, top].  score_fn: 0 softmax over all experts, 1 sigmoid, 2 the `top` largest logits are chosen and
 // their weights are the softmax over the chosen logits only.  `bias` (float32 [E], optional) is added to the
 // logits.  With `shared_w` (float32 [tokens]) the router matrix has one more row, the gate of an expert that
-// every token uses: shared_w[t] = sigmoid(Wr[E] . x).  One block per token: its four warps share out the experts
-// (each sum runs over a lane's stride of the row, then over the lanes: an order that depends on the sizes
-// only), then the first warp scores and picks.
+// every token uses: shared_w[t] = sigmoid(Wr[E] . x).  One block per token: its eight warps share out the experts
+// (the token's row waits in shared memory as float32), then the first warp scores and picks.
+#define MOE_ROUTER_THREADS 256
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(MOE_ROUTER_THREADS)
 moe_router_kernel(const T* __restrict__ x, long x_stride, const float* __restrict__ Wr, const float* __restrict__ bias,
                   float* __restrict__ gates, int* __restrict__ top_idx, float* __restrict__ top_w,
                   float* __restrict__ shared_w, int num_tokens, int hidden, int E, int top, int score_fn,
                   int renormalize) {
   __shared__ float z[MOE_MAX_E + 2];
+  extern __shared__ __align__(16) float xrow[];          // the token's row as float32 [hidden]
   LL_PDL_TRIGGER();
   LL_PDL_WAIT();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const T* xr = x + (size_t)t * x_stride;
+  for (int i = threadIdx.x; i < hidden; i += MOE_ROUTER_THREADS) xrow[i] = to_f32<T>(xr[i]);
+  __syncthreads();
   const int n_rows = E + (shared_w ? 1 : 0);
-  for (int e0 = warp * 2; e0 < n_rows; e0 += 8) {      // two experts a pass: one read of x for two sums
-    const bool two = e0 + 1 < n_rows;
-    const float* w0 = Wr + (size_t)e0 * hidden;
-    const float* w1 = Wr + (size_t)(two ? e0 + 1 : e0) * hidden;
-    float a0 = 0.f, a1 = 0.f;
-#pragma unroll 8
-    for (int i = lane; i < hidden; i += 32) {
-      const float xv = to_f32<T>(xr[i]);
-      a0 = fmaf(w0[i], xv, a0);
-      a1 = fmaf(w1[i], xv, a1);
+  // a warp a row: a lane sums its pieces of four numbers (four sums side by side), then the lanes are added up:
+  // an order that depends on the sizes only
+  const bool vec = (hidden & 3) == 0;
+  for (int e = warp; e < n_rows; e += MOE_ROUTER_THREADS / 32) {
+    const float* wrow = Wr + (size_t)e * hidden;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    if (vec) {
+#pragma unroll 4
+      for (int i = 4 * lane; i < hidden; i += 128) {
+        const float4 w4 = *reinterpret_cast<const float4*>(wrow + i);
+        const float4 x4 = *reinterpret_cast<const float4*>(xrow + i);
+        a0 = fmaf(w4.x, x4.x, a0);
+        a1 = fmaf(w4.y, x4.y, a1);
+        a2 = fmaf(w4.z, x4.z, a2);
+        a3 = fmaf(w4.w, x4.w, a3);
+      }
+    } else {
+#pragma unroll 4
+      for (int i = lane; i < hidden; i += 32) a0 = fmaf(wrow[i], xrow[i], a0);
     }
-    a0 = warp_sum(a0);
-    a1 = warp_sum(a1);
-    if (lane == 0) {
-      z[e0] = a0 + ((bias && e0 < E) ? bias[e0] : 0.f);
-      if (two) z[e0 + 1] = a1 + ((bias && e0 + 1 < E) ? bias[e0 + 1] : 0.f);
-    }
+    const float a = warp_sum((a0 + a1) + (a2 + a3));
+    if (lane == 0) z[e] = a + ((bias && e < E) ? bias[e] : 0.f);
   }
   __syncthreads();
   if (warp != 0) return;
@@ -179,7 +187,9 @@ extern "C" int ll_moe_router(int dtype, const void* x, long x_stride, const floa
                              int score_fn, int renormalize, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (E <= 0 || E > MOE_MAX_E || top <= 0 || top > E || hidden <= 0) return (int)cudaErrorInvalidValue;
-  LL_DISPATCH_DTYPE(dtype, ll_launch(moe_router_kernel<T>, dim3(num_tokens), dim3(128), 0, stream,
+  const size_t smem = sizeof(float) * (size_t)((hidden + 3) / 4 * 4);
+  if (smem > 40 * 1024) return (int)cudaErrorInvalidValue;      // (rows of up to 10,240 numbers)
+  LL_DISPATCH_DTYPE(dtype, ll_launch(moe_router_kernel<T>, dim3(num_tokens), dim3(MOE_ROUTER_THREADS), smem, stream,
                                      (const T*)x, x_stride, Wr, bias, gates, top_idx, top_w, shared_w, num_tokens,
                                      hidden, E, top, score_fn, renormalize));
   return LL_LAUNCH_RESULT();
@@ -400,17 +410,31 @@ __global__ void moe_gated_act_kernel(T* __restrict__ out, const T* __restrict__ 
 }
 
 // in: T [rows, 2 * ff] (gate columns, then up columns); out: T [rows, ff] = activation times row_w[row].
-template <typename T>
+// A thread takes VEC neighbouring units of a row (16-byte accesses where the width allows it).
+template <typename T, int VEC>
 __global__ void moe_row_gated_act_kernel(T* __restrict__ out, const T* __restrict__ in, const float* __restrict__ row_w,
-                                         long total, int ff, float limit, float alpha) {
+                                         long total_vec, int ff, float limit, float alpha) {
   LL_PDL_WAIT();      // (no early release: what runs next may be a library kernel that does not wait itself)
   const long step = (long)gridDim.x * blockDim.x;
-  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += step) {
-    const long r = idx / ff;
-    const int j = (int)(idx - r * ff);
+  const int per_row = ff / VEC;
+  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total_vec; idx += step) {
+    const long r = idx / per_row;
+    const int j = (int)(idx - r * per_row) * VEC;
     const float w = row_w ? row_w[r] : 1.f;
-    const T* p = in + (size_t)r * 2 * ff;
-    out[idx] = from_f32<T>(clamped_swish_gate(to_f32<T>(p[j]), to_f32<T>(p[ff + j]), limit, alpha) * w);
+    const T* p = in + (size_t)r * 2 * ff + j;
+    T g[VEC], u[VEC], y[VEC];
+    if (VEC > 1) {
+      *reinterpret_cast<uint4*>(g) = *reinterpret_cast<const uint4*>(p);
+      *reinterpret_cast<uint4*>(u) = *reinterpret_cast<const uint4*>(p + ff);
+    } else {
+      g[0] = p[0];
+      u[0] = p[ff];
+    }
+#pragma unroll
+    for (int k = 0; k < VEC; ++k)
+      y[k] = from_f32<T>(clamped_swish_gate(to_f32<T>(g[k]), to_f32<T>(u[k]), limit, alpha) * w);
+    if (VEC > 1) *reinterpret_cast<uint4*>(out + (size_t)r * ff + j) = *reinterpret_cast<const uint4*>(y);
+    else out[(size_t)r * ff + j] = y[0];
   }
 }
 
@@ -430,9 +454,19 @@ extern "C" int ll_moe_gated_act(int dtype, void* out, const void* in, const floa
 extern "C" int ll_moe_row_gated_act(int dtype, void* out, const void* in, const float* row_w, int rows, int ff,
                                     float limit, float alpha, int sms, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  const long total = (long)rows * ff;
-  const long most = (long)(sms > 0 ? sms : 148) * 16, want = (total + 255) / 256;
-  LL_DISPATCH_DTYPE(dtype, ll_launch(moe_row_gated_act_kernel<T>, dim3((int)(want < most ? want : most)), dim3(256), 0,
-                                     stream, (T*)out, (const T*)in, row_w, total, ff, limit, alpha));
+  const long most = (long)(sms > 0 ? sms : 148) * 16;
+  LL_DISPATCH_DTYPE(dtype, {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    const bool wide = (ff % VEC) == 0 && ((uintptr_t)in % 16) == 0 && ((uintptr_t)out % 16) == 0;
+    const long total = (long)rows * ff / (wide ? VEC : 1);
+    const long want = (total + 255) / 256;
+    const int blocks = (int)(want < most ? want : most);
+    if (wide)
+      ll_launch(moe_row_gated_act_kernel<T, VEC>, dim3(blocks), dim3(256), 0, stream, (T*)out, (const T*)in, row_w,
+                total, ff, limit, alpha);
+    else
+      ll_launch(moe_row_gated_act_kernel<T, 1>, dim3(blocks), dim3(256), 0, stream, (T*)out, (const T*)in, row_w, total,
+                ff, limit, alpha);
+  });
   return LL_LAUNCH_RESULT();
 }

@@ -1,11 +1,15 @@
 // Two mixers side by side, joined: out = (rms(a + bias_a) * wa + rms(b) * wb) / 2, each RMS norm over the whole
-// row (x / sqrt(mean(x^2) + eps), float32).  One block per token; the rows are read twice (the second time
-// from L1/L2).  `bias_a` (float32, optional) is the first mixer's output bias, added here instead of in a
+// row (x / sqrt(mean(x^2) + eps), float32).  One block per token; a thread keeps its pieces of both rows in
+// registers between the sums of squares and the output (rows of up to 256 x PIECES x VEC numbers; longer rows are
+// read a second time).  `bias_a` (float32, optional) is the first mixer's output bias, added here instead of in a
 // pass of its own.
 #include "common.cuh"
 
-template <typename T>
-__global__ void __launch_bounds__(256)
+#define NJ_THREADS 256
+#define NJ_PIECES 4
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(NJ_THREADS)
 rms_pair_mean_kernel(T* __restrict__ out, const T* __restrict__ a, long a_stride, const float* __restrict__ bias_a,
                      const float* __restrict__ wa, const T* __restrict__ b, long b_stride, const float* __restrict__ wb,
                      float eps, int width) {
@@ -15,21 +19,69 @@ rms_pair_mean_kernel(T* __restrict__ out, const T* __restrict__ a, long a_stride
   const int t = blockIdx.x;
   const T* ar = a + (size_t)t * a_stride;
   const T* br = b + (size_t)t * b_stride;
+  const bool resident = width <= NJ_THREADS * NJ_PIECES * VEC;
+  float xa[NJ_PIECES][VEC], xb[NJ_PIECES][VEC];
   float sa = 0.f, sb = 0.f;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    const float x = to_f32<T>(ar[i]) + (bias_a ? bias_a[i] : 0.f);
-    const float y = to_f32<T>(br[i]);
-    sa = fmaf(x, x, sa);
-    sb = fmaf(y, y, sb);
+  auto load = [&](int c, float* x, float* y) {
+    T va[VEC], vb[VEC];
+    if (VEC > 1) {
+      *reinterpret_cast<uint4*>(va) = *reinterpret_cast<const uint4*>(ar + c);
+      *reinterpret_cast<uint4*>(vb) = *reinterpret_cast<const uint4*>(br + c);
+    } else {
+      va[0] = ar[c];
+      vb[0] = br[c];
+    }
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      x[k] = to_f32<T>(va[k]) + (bias_a ? bias_a[c + k] : 0.f);
+      y[k] = to_f32<T>(vb[k]);
+    }
+  };
+  if (resident) {
+#pragma unroll
+    for (int p = 0; p < NJ_PIECES; ++p) {
+      const int c = (threadIdx.x + p * NJ_THREADS) * VEC;
+      if (c < width) {
+        load(c, xa[p], xb[p]);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          sa = fmaf(xa[p][k], xa[p][k], sa);
+          sb = fmaf(xb[p][k], xb[p][k], sb);
+        }
+      }
+    }
+  } else {
+    for (int c = threadIdx.x * VEC; c < width; c += NJ_THREADS * VEC) {
+      load(c, xa[0], xb[0]);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        sa = fmaf(xa[0][k], xa[0][k], sa);
+        sb = fmaf(xb[0][k], xb[0][k], sb);
+      }
+    }
   }
   sa = block_sum(sa, scratch);
   sb = block_sum(sb, scratch);
   const float ia = 1.0f / sqrtf(sa / (float)width + eps);
   const float ib = 1.0f / sqrtf(sb / (float)width + eps);
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    const float x = to_f32<T>(ar[i]) + (bias_a ? bias_a[i] : 0.f);
-    const float y = to_f32<T>(br[i]);
-    out[(size_t)t * width + i] = from_f32<T>(0.5f * (x * ia * wa[i] + y * ib * wb[i]));
+  auto store = [&](int c, const float* x, const float* y) {
+    T vo[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) vo[k] = from_f32<T>(0.5f * (x[k] * ia * wa[c + k] + y[k] * ib * wb[c + k]));
+    if (VEC > 1) *reinterpret_cast<uint4*>(out + (size_t)t * width + c) = *reinterpret_cast<const uint4*>(vo);
+    else out[(size_t)t * width + c] = vo[0];
+  };
+  if (resident) {
+#pragma unroll
+    for (int p = 0; p < NJ_PIECES; ++p) {
+      const int c = (threadIdx.x + p * NJ_THREADS) * VEC;
+      if (c < width) store(c, xa[p], xb[p]);
+    }
+  } else {
+    for (int c = threadIdx.x * VEC; c < width; c += NJ_THREADS * VEC) {
+      load(c, xa[0], xb[0]);
+      store(c, xa[0], xb[0]);
+    }
   }
 }
 
@@ -37,7 +89,16 @@ extern "C" int ll_rms_pair_mean(int dtype, void* out, const void* a, long a_stri
                                 const float* wa, const void* b, long b_stride, const float* wb, float eps,
                                 int num_tokens, int width, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
-  LL_DISPATCH_DTYPE(dtype, ll_launch(rms_pair_mean_kernel<T>, dim3(num_tokens), dim3(256), 0, stream, (T*)out,
-                                     (const T*)a, a_stride, bias_a, wa, (const T*)b, b_stride, wb, eps, width));
+  LL_DISPATCH_DTYPE(dtype, {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    const bool wide = (width % VEC) == 0 && (a_stride % VEC) == 0 && (b_stride % VEC) == 0 &&
+                      ((uintptr_t)a % 16) == 0 && ((uintptr_t)b % 16) == 0 && ((uintptr_t)out % 16) == 0;
+    if (wide)
+      ll_launch(rms_pair_mean_kernel<T, VEC>, dim3(num_tokens), dim3(NJ_THREADS), 0, stream, (T*)out, (const T*)a,
+                a_stride, bias_a, wa, (const T*)b, b_stride, wb, eps, width);
+    else
+      ll_launch(rms_pair_mean_kernel<T, 1>, dim3(num_tokens), dim3(NJ_THREADS), 0, stream, (T*)out, (const T*)a,
+                a_stride, bias_a, wa, (const T*)b, b_stride, wb, eps, width);
+  });
   return LL_LAUNCH_RESULT();
 }

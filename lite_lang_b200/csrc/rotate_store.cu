@@ -10,8 +10,81 @@
 //   * q (and k, v) are written back in place, rounded once; k and v also go to the token's cache slot.
 // No table of positions, so no position is out of range.
 //
+// With interleaved pairs and even sizes a pair is one access (two neighbouring values of the storage type), and
+// so are two neighbouring values of a head's unrotated tail and of v.
+//
 // Cache plane: K [num_pages, nkv, page_size, hd], V [num_pages, nkv, page_size, vd].
 #include "common.cuh"
+
+template <typename T> struct Pair;
+template <> struct Pair<float> { typedef float2 type; };
+template <> struct Pair<bf16> { typedef __nv_bfloat162 type; };
+template <typename T> __device__ __forceinline__ float2 pair_to_f32(typename Pair<T>::type v);
+template <> __device__ __forceinline__ float2 pair_to_f32<float>(float2 v) { return v; }
+template <> __device__ __forceinline__ float2 pair_to_f32<bf16>(__nv_bfloat162 v) { return __bfloat1622float2(v); }
+template <typename T> __device__ __forceinline__ typename Pair<T>::type pair_from_f32(float x, float y);
+template <> __device__ __forceinline__ float2 pair_from_f32<float>(float x, float y) { return make_float2(x, y); }
+template <> __device__ __forceinline__ __nv_bfloat162 pair_from_f32<bf16>(float x, float y) {
+  return __floats2bfloat162_rn(x, y);
+}
+
+// interleaved pairs; hd, vd, rot_dim, the row stride and all offsets even, so every pair of neighbours is aligned
+template <typename T>
+__global__ void __launch_bounds__(256)
+bias_rotate_store_pairs_kernel(T* __restrict__ qkv, long qkv_stride, const float* __restrict__ bias,
+                               const int* __restrict__ positions, const float* __restrict__ freq, int rot_dim, int nh,
+                               int nkv, int hd, int vd, const int* __restrict__ slot_map, T* __restrict__ k_cache,
+                               T* __restrict__ v_cache, int page_size, long num_slots, int* status) {
+  typedef typename Pair<T>::type P2;
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const int t = blockIdx.x;
+  T* row = qkv + (size_t)t * qkv_stride;
+  const float pos = (float)(positions ? positions[t] : 0);
+  long slot = slot_map ? (long)slot_map[t] : -1;
+  if (slot >= num_slots) {
+    if (threadIdx.x == 0) set_status(status, LL_ERR_SLOT_RANGE);
+    slot = -1;
+  }
+  const long page = slot >= 0 ? slot / page_size : 0;
+  const int off = slot >= 0 ? (int)(slot - page * page_size) : 0;
+  const int half = rot_dim >> 1, hp = hd >> 1, vp = vd >> 1;
+  const int qk_pairs = (nh + nkv) * hp;
+  for (int w = threadIdx.x; w < qk_pairs + nkv * vp; w += blockDim.x) {
+    if (w < qk_pairs) {
+      const int h = w / hp, i = w - h * hp;
+      const size_t at = (size_t)h * hd + 2 * i;
+      float2 x = pair_to_f32<T>(*reinterpret_cast<const P2*>(row + at));
+      if (bias) {
+        const float2 b2 = *reinterpret_cast<const float2*>(bias + at);
+        x.x += b2.x;
+        x.y += b2.y;
+      }
+      if (i < half) {
+        const float a = pos * freq[i];
+        const float c = cosf(a), s = sinf(a);
+        x = make_float2(x.x * c - x.y * s, x.y * c + x.x * s);
+      }
+      const P2 r = pair_from_f32<T>(x.x, x.y);
+      *reinterpret_cast<P2*>(row + at) = r;
+      if (h >= nh && slot >= 0)
+        *reinterpret_cast<P2*>(k_cache + (((size_t)page * nkv + (h - nh)) * page_size + off) * hd + 2 * i) = r;
+    } else {
+      const int u = w - qk_pairs;
+      const int h = u / vp, j = 2 * (u - h * vp);
+      const size_t at = (size_t)(nh + nkv) * hd + (size_t)h * vd + j;
+      float2 x = pair_to_f32<T>(*reinterpret_cast<const P2*>(row + at));
+      if (bias) {
+        const float2 b2 = *reinterpret_cast<const float2*>(bias + at);
+        x.x += b2.x;
+        x.y += b2.y;
+      }
+      const P2 r = pair_from_f32<T>(x.x, x.y);
+      if (bias) *reinterpret_cast<P2*>(row + at) = r;
+      if (slot >= 0) *reinterpret_cast<P2*>(v_cache + (((size_t)page * nkv + h) * page_size + off) * vd + j) = r;
+    }
+  }
+}
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -86,8 +159,19 @@ extern "C" int ll_bias_rotate_store(int dtype, void* qkv, long qkv_stride, const
                                     int num_tokens, int* status, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || hd <= 0 || vd <= 0) return (int)cudaErrorInvalidValue;
-  LL_DISPATCH_DTYPE(dtype, ll_launch(bias_rotate_store_kernel<T>, dim3(num_tokens), dim3(256), 0, stream, (T*)qkv,
-                                     qkv_stride, bias, positions, freq, rot_dim, interleaved, nh, nkv, hd, vd, slot_map,
-                                     (T*)k_cache, (T*)v_cache, page_size, num_slots, status));
+  const int esz = dtype == LL_DTYPE_F32 ? 4 : 2;
+  const bool pairs = (interleaved || rot_dim == 0) && (hd % 2) == 0 && (vd % 2) == 0 && (qkv_stride % 2) == 0 &&
+                     ((uintptr_t)qkv % (2 * esz)) == 0 && ((uintptr_t)bias % 8) == 0 &&
+                     ((uintptr_t)k_cache % (2 * esz)) == 0 && ((uintptr_t)v_cache % (2 * esz)) == 0;
+  LL_DISPATCH_DTYPE(dtype, {
+    if (pairs)
+      ll_launch(bias_rotate_store_pairs_kernel<T>, dim3(num_tokens), dim3(256), 0, stream, (T*)qkv, qkv_stride, bias,
+                positions, freq, rot_dim, nh, nkv, hd, vd, slot_map, (T*)k_cache, (T*)v_cache, page_size, num_slots,
+                status);
+    else
+      ll_launch(bias_rotate_store_kernel<T>, dim3(num_tokens), dim3(256), 0, stream, (T*)qkv, qkv_stride, bias,
+                positions, freq, rot_dim, interleaved, nh, nkv, hd, vd, slot_map, (T*)k_cache, (T*)v_cache, page_size,
+                num_slots, status);
+  });
   return LL_LAUNCH_RESULT();
 }

@@ -33,8 +33,8 @@ __global__ void embed_streams_kernel(float* __restrict__ out, const T* __restric
 // One block per output row i (token r = rows ? rows[i] : i).  A thread takes VEC neighbouring columns.
 // y: T [tokens, hidden] or null; y_parts: float32 [parts, tokens, hidden] partial sums of a split product, or null;
 // mix [S, S] (from, to), write [S], read [S] (null: all ones), alpha [1], w, b [hidden] (b null: none): float32.
-template <typename T, int VEC>
-__global__ void __launch_bounds__(256)
+template <typename T, int VEC, int SM>      // SM: the most streams this instance takes (its register arrays)
+__global__ void __launch_bounds__(128)
 stream_tanh_norm_kernel(T* __restrict__ out, float* __restrict__ X, const T* __restrict__ y,
                         const float* __restrict__ y_parts, int parts, long part_stride, const float* __restrict__ mix,
                         const float* __restrict__ write, const float* __restrict__ read,
@@ -55,9 +55,9 @@ stream_tanh_norm_kernel(T* __restrict__ out, float* __restrict__ X, const T* __r
   const int r = rows ? rows[i] : i;
   float* xr = X + (size_t)r * S * hidden;
   for (int c = threadIdx.x * VEC; c < hidden; c += blockDim.x * VEC) {
-    float xs[ST_MAX][VEC];
+    float xs[SM][VEC];
 #pragma unroll
-    for (int s = 0; s < ST_MAX; ++s) {
+    for (int s = 0; s < SM; ++s) {
       if (s < S) {
         if (VEC == 4) {
           const float4 v = *reinterpret_cast<const float4*>(xr + (size_t)s * hidden + c);
@@ -69,28 +69,36 @@ stream_tanh_norm_kernel(T* __restrict__ out, float* __restrict__ X, const T* __r
     }
     if (pending) {
       float yv[VEC];
+      if (y) {       // (VEC numbers of y in one access: the launcher checked its alignment)
+        T raw[VEC];
+        if (VEC == 4 && sizeof(T) == 2) *reinterpret_cast<uint2*>(raw) = *reinterpret_cast<const uint2*>(y + (size_t)r * hidden + c);
+        else if (VEC == 4) *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(y + (size_t)r * hidden + c);
+        else raw[0] = y[(size_t)r * hidden + c];
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        float v = y ? to_f32<T>(y[(size_t)r * hidden + c + k]) : 0.f;
-        for (int p = 0; p < parts; ++p) v += y_parts[(size_t)p * part_stride + (size_t)r * hidden + c + k];
-        yv[k] = v;
+        for (int k = 0; k < VEC; ++k) yv[k] = to_f32<T>(raw[k]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) yv[k] = 0.f;
       }
-      float nx[ST_MAX][VEC];
+      for (int p = 0; p < parts; ++p)
 #pragma unroll
-      for (int t = 0; t < ST_MAX; ++t) {
+        for (int k = 0; k < VEC; ++k) yv[k] += y_parts[(size_t)p * part_stride + (size_t)r * hidden + c + k];
+      float nx[SM][VEC];
+#pragma unroll
+      for (int t = 0; t < SM; ++t) {
         if (t < S) {
 #pragma unroll
           for (int k = 0; k < VEC; ++k) {
             float v = 0.f;
 #pragma unroll
-            for (int s = 0; s < ST_MAX; ++s)
+            for (int s = 0; s < SM; ++s)
               if (s < S) v = fmaf(s_mix[s * S + t], xs[s][k], v);
             nx[t][k] = fmaf(s_write[t], yv[k], v);
           }
         }
       }
 #pragma unroll
-      for (int t = 0; t < ST_MAX; ++t) {
+      for (int t = 0; t < SM; ++t) {
         if (t < S) {
 #pragma unroll
           for (int k = 0; k < VEC; ++k) xs[t][k] = nx[t][k];
@@ -104,15 +112,18 @@ stream_tanh_norm_kernel(T* __restrict__ out, float* __restrict__ X, const T* __r
         }
       }
     }
+    T res[VEC];
 #pragma unroll
     for (int k = 0; k < VEC; ++k) {
       float u = 0.f;
 #pragma unroll
-      for (int s = 0; s < ST_MAX; ++s)
+      for (int s = 0; s < SM; ++s)
         if (s < S) u = fmaf(s_read[s], xs[s][k], u);
-      const float v = tanhf(a * u) * w[c + k] + (b ? b[c + k] : 0.f);
-      out[(size_t)i * hidden + c + k] = from_f32<T>(v);
+      res[k] = from_f32<T>(tanhf(a * u) * w[c + k] + (b ? b[c + k] : 0.f));
     }
+    if (VEC == 4 && sizeof(T) == 2) *reinterpret_cast<uint2*>(out + (size_t)i * hidden + c) = *reinterpret_cast<const uint2*>(res);
+    else if (VEC == 4) *reinterpret_cast<uint4*>(out + (size_t)i * hidden + c) = *reinterpret_cast<const uint4*>(res);
+    else out[(size_t)i * hidden + c] = res[0];
   }
 }
 
@@ -144,17 +155,23 @@ extern "C" int ll_stream_tanh_norm(int dtype, void* out, float* X, const void* y
                                    int S, int hidden, int n_out, cudaStream_t stream) {
   if (n_out <= 0) return 0;
   if (S <= 0 || S > ST_MAX || hidden <= 0) return (int)cudaErrorInvalidValue;
-  const bool wide = (hidden % 4) == 0 && ((uintptr_t)X % 16) == 0;
-  const int per = wide ? hidden / 4 : hidden;
-  const int threads = per >= 256 ? 256 : per >= 128 ? 128 : 64;
+  const bool wide = (hidden % 4) == 0 && ((uintptr_t)X % 16) == 0 && ((uintptr_t)out % 16) == 0 &&
+                    ((uintptr_t)y % 16) == 0;
+#define ST_LAUNCH(VV, MM)                                                                                            \
+  ll_launch(stream_tanh_norm_kernel<T, VV, MM>, dim3(n_out), dim3(128), 0, stream, (T*)out, X, (const T*)y, y_parts, \
+            parts, part_stride, mix, write, read, alpha, w, b, rows, write_back, S, hidden)
   LL_DISPATCH_DTYPE(dtype, {
-    if (wide)
-      ll_launch(stream_tanh_norm_kernel<T, 4>, dim3(n_out), dim3(threads), 0, stream, (T*)out, X, (const T*)y, y_parts,
-                parts, part_stride, mix, write, read, alpha, w, b, rows, write_back, S, hidden);
-    else
-      ll_launch(stream_tanh_norm_kernel<T, 1>, dim3(n_out), dim3(threads), 0, stream, (T*)out, X, (const T*)y, y_parts,
-                parts, part_stride, mix, write, read, alpha, w, b, rows, write_back, S, hidden);
+    if (wide) {
+      if (S <= 2) ST_LAUNCH(4, 2);
+      else if (S <= 4) ST_LAUNCH(4, 4);
+      else ST_LAUNCH(4, ST_MAX);
+    } else {
+      if (S <= 2) ST_LAUNCH(1, 2);
+      else if (S <= 4) ST_LAUNCH(1, 4);
+      else ST_LAUNCH(1, ST_MAX);
+    }
   });
+#undef ST_LAUNCH
   return LL_LAUNCH_RESULT();
 }
 

@@ -595,7 +595,8 @@ def smallm_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and weight.is_contiguous() and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
-def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False) -> torch.Tensor:
+def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False,
+                act: str = "silu") -> torch.Tensor:
     """out = x @ weight.T for up to 64 tokens with the weight-streaming kernel.
 
     ``gated``: weight holds gate rows then up rows ([2 I, K]); out [M, I] = silu(gate) * up.
@@ -611,7 +612,8 @@ def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated:
           "gemm_smallm: out dtype")
     load_library("gemm_smallm").call(
         "ll_gemm_smallm", _ptr(out), c_long(out.stride(0)), c_int(1 if out.dtype == torch.float32 else 0), _ptr(x),
-        c_long(x.stride(0)), _ptr(weight), c_int(m), c_int(n), c_int(k), c_int(1 if gated else 0), _stream())
+        c_long(x.stride(0)), _ptr(weight), c_int(m), c_int(n), c_int(k), c_int(1 + GATE_ACT[act] if gated else 0),
+        _stream())
     return out
 
 
@@ -667,7 +669,7 @@ def stream_ksplit(n: int, k: int, mode: int, device) -> int:
 
 
 def gemm_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: int,
-                status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                status: Optional[torch.Tensor] = None, act: str = "silu") -> torch.Tensor:
     """out = x @ weight.T for up to 32 bfloat16 tokens (64 for mode 2 to bfloat16 with k whole) with the TMA
     weight-streaming kernel.
 
@@ -694,8 +696,8 @@ def gemm_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: 
     _need(out.dtype == torch.bfloat16 or (out.dtype == torch.float32 and not gated), "gemm_stream: out dtype")
     load_library("gemm_stream").call(
         "ll_gemm_stream", _ptr(out), c_long(out_stride), c_int(1 if out.dtype == torch.float32 else 0), _ptr(x),
-        c_long(x.stride(0)), _ptr(weight), c_int(m), c_int(n), c_int(k), c_int(mode), c_int(ksplit),
-        c_int(sm_count(x.device)), _ptr(status if status is not None else TIMELINE_STATUS), _stream())
+        c_long(x.stride(0)), _ptr(weight), c_int(m), c_int(n), c_int(k), c_int(mode | (GATE_ACT[act] << 8)),
+        c_int(ksplit), c_int(sm_count(x.device)), _ptr(status if status is not None else TIMELINE_STATUS), _stream())
     return out
 
 
@@ -851,7 +853,7 @@ def tc_ksplit(n: int, k: int, device) -> int:
     return (boxes + per - 1) // per
 
 
-def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False,
+def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False, act: str = "silu",
             status: Optional[torch.Tensor] = None, sumsq: Optional[torch.Tensor] = None, eps: float = 0.0) -> torch.Tensor:
     """out = x @ weight.T for up to 128 bfloat16 tokens on the tcgen05 tensor cores (weights streamed
     by TMA, accumulator in tensor memory).  ``gated``: weight is [2 I, K] and out = silu(gate) * up.
@@ -874,7 +876,8 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: boo
     _need(out.dtype == torch.bfloat16 or (out.dtype == torch.float32 and not gated), "gemm_tc: out dtype")
     load_library("gemm_tc").call(
         "ll_gemm_tc", _ptr(out), c_long(out_stride), c_int(1 if out.dtype == torch.float32 else 0), _ptr(x),
-        c_long(x.stride(0)), _ptr(weight), c_int(m), c_int(n), c_int(k), c_int(1 if gated else 0), c_int(ksplit),
+        c_long(x.stride(0)), _ptr(weight), c_int(m), c_int(n), c_int(k), c_int(1 + GATE_ACT[act] if gated else 0),
+        c_int(ksplit),
         c_int(sm_count(x.device)), _ptr(sumsq), c_int(0 if sumsq is None else sumsq.shape[0]), c_float(eps),
         _ptr(status if status is not None else TIMELINE_STATUS), _stream())
     return out
@@ -893,7 +896,7 @@ def pair_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def gemm_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False,
-              status: Optional[torch.Tensor] = None) -> torch.Tensor:
+              status: Optional[torch.Tensor] = None, act: str = "silu") -> torch.Tensor:
     """out = x @ weight.T for many bfloat16 tokens on the tcgen05 tensor cores, a pair of SMs a tile of
     256 tokens x 256 columns.  ``gated``: weight is [2 I, K] and out = silu(gate) * up, the activation done
     on the accumulator, so gate and up never go to memory."""
@@ -905,7 +908,8 @@ def gemm_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: b
           and out.stride(1) == 1, "gemm_pair: out is bfloat16 [M, N] with unit column stride")
     load_library("gemm_pair").call(
         "ll_gemm_pair", _ptr(out), c_long(out.stride(0)), _ptr(x), c_long(x.stride(0)), _ptr(weight), c_int(m),
-        c_int(n), c_int(k), c_int(1 if gated else 0), c_int(sm_count(x.device)), _ptr(status), _stream())
+        c_int(n), c_int(k), c_int(1 + GATE_ACT[act] if gated else 0), c_int(sm_count(x.device)), _ptr(status),
+        _stream())
     return out
 
 
@@ -975,20 +979,23 @@ def linear_accumulate(x: torch.Tensor, weight: torch.Tensor, acc: torch.Tensor) 
     torch.addmm(acc, x, weight.t(), out=acc)
 
 
-def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
-    """silu(x @ Wg.T) * (x @ Wu.T) with W = [Wg; Wu]: fused for few tokens, else product + kernel."""
+def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """act(x @ Wg.T) * (x @ Wu.T) with W = [Wg; Wu], act SiLU or ReLU: fused for few tokens, else product + kernel."""
     inter = w_gate_up.shape[0] // 2
     act = torch.empty((x.shape[0], inter), dtype=x.dtype, device=x.device)
     if tc_preferred(x, w_gate_up, gated=True):
-        return gemm_tc(x, w_gate_up, act, gated=True)
+        return gemm_tc(x, w_gate_up, act, gated=True, act=activation)
     if stream_mode(x, w_gate_up, gated=True) is not None:
-        return gemm_stream(x, w_gate_up, act, 1)
+        return gemm_stream(x, w_gate_up, act, 1, act=activation)
     if smallm_preferred(x, w_gate_up, gated=True):
-        return gemm_smallm(x, w_gate_up, act, gated=True)
+        return gemm_smallm(x, w_gate_up, act, gated=True, act=activation)
     if TC_ENABLED and x.shape[0] >= PAIR_MIN_M and pair_supported(x, w_gate_up):
-        return gemm_pair(x, w_gate_up, act, gated=True)
+        return gemm_pair(x, w_gate_up, act, gated=True, act=activation)
     gu = linear(x, w_gate_up)
-    silu_mul(act, gu)
+    if activation == "silu":
+        silu_mul(act, gu)
+    else:
+        act_mul(act, gu, activation)
     return act
 
 
@@ -1449,11 +1456,19 @@ def stream_sum(X: torch.Tensor, streams: int) -> torch.Tensor:
 # --------------------------------------------------------------------------
 # linear attention with a decay per head
 # --------------------------------------------------------------------------
+def silu_rows(x: torch.Tensor) -> None:
+    """x <- silu(x) in place (x may be a slice of columns of a wider matrix); float32 arithmetic, one rounding."""
+    _need_cuda(x)
+    _need(x.dim() == 2 and x.stride(1) == 1, "silu_rows: rows with unit column stride")
+    load_library("linear_attn").call("ll_silu_rows", c_int(_dtype_code(x)), _ptr(x), c_long(x.stride(0)),
+                                     c_int(x.shape[0]), c_int(x.shape[1]), c_int(sm_count(x.device)), _stream())
+
+
 def decay_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor, state: torch.Tensor,
                step, o: torch.Tensor, H: int, dk: int, dv: int, write_state: bool = True) -> None:
-    """S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t for every entry's tokens in order, q, k, v = SiLU of the
-    columns of ``proj`` at the three offsets; ``state`` float32 [slots, H * dv * dk] goes on from where the
-    request stopped; ``o`` float32 [tokens, H * dv]."""
+    """S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t for every entry's tokens in order; q, k, v are the
+    columns of ``proj`` at the three offsets (already activated); ``state`` float32 [slots, H * dv * dk] goes on
+    from where the request stopped; ``o`` float32 [tokens, H * dv]."""
     _need_cuda(proj, decay, state, o)
     _f32(decay, "decay")
     _f32(state, "state")

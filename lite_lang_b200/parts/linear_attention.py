@@ -80,6 +80,7 @@ class DecayLinearAttention(Mixer):
     def forward(self, x, step, cache):
         n, dev = x.shape[0], x.device
         proj = ops.linear(x, self.w_in)
+        ops.silu_rows(proj[:, :self.off["g"]])        # q | k | v (and the zero columns that pad them)
         o = torch.empty((n, self.Cv), dtype=torch.float32, device=dev)
         ops.decay_scan(proj, self.off["q"], self.off["k"], self.off["v"], self.decay, cache.state, step, o,
                        self.H, self.dk, self.dv, cache.writable)

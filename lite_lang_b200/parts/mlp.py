@@ -63,13 +63,8 @@ class GatedMLP(FeedForward):
     def forward(self, x, step, residual=None):
         if isinstance(x, NormSplit):    # the norm before this part, left to its first product
             act = ops.gemm_stream_gated_scaled(x.scaled, self.w_gate_up, x.sumsq, x.eps, step.status)
-        elif self.activation == "silu":
-            act = ops.gated_linear(x, self.w_gate_up)
         else:
-            # (the products with the activation in their epilogue are SiLU ones)
-            gu = ops.linear(x, self.w_gate_up)
-            act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
-            ops.act_mul(act, gu, self.activation)
+            act = ops.gated_linear(x, self.w_gate_up, self.activation)
         if residual is not None and ops.accumulate_preferred(act, self.w_down):
             ops.linear_accumulate(act, self.w_down, residual)
             return None

@@ -306,10 +306,12 @@ def test_attention_with_values_wider_or_narrower_than_keys(dtype, nh, nkv, hd, v
     assert float((last[0] - vs[0][far[0], 0]).abs().max()) < 0.5 * float(vs[0][far[0], 0].abs().max())
 
 
-def _scan_reference(proj, off, H, dk, dv, decay):
-    q = P.silu(proj[:, off[0]:off[0] + H * dk]).view(-1, H, dk)
-    k = P.silu(proj[:, off[1]:off[1] + H * dk]).view(-1, H, dk)
-    v = P.silu(proj[:, off[2]:off[2] + H * dv]).view(-1, H, dv)
+def _scan_reference(proj, off, H, dk, dv, decay, dtype):
+    """(The activated q, k, v are kept in the engine's dtype between the two kernels: rounded here as there.)"""
+    act = lambda z: P.silu(z).to(dtype).double()
+    q = act(proj[:, off[0]:off[0] + H * dk]).view(-1, H, dk)
+    k = act(proj[:, off[1]:off[1] + H * dk]).view(-1, H, dk)
+    v = act(proj[:, off[2]:off[2] + H * dv]).view(-1, H, dv)
     o = torch.stack([P.decay_recurrence(q[:, h], k[:, h], v[:, h], decay[h])[0] for h in range(H)], dim=1)
     return o.reshape(-1, H * dv)
 
@@ -325,7 +327,7 @@ def test_decay_scan_in_portions_side_by_side_and_in_slots_used_again(dtype, H, d
     width = off[2] + H * dv + 5
     lens = [70, 33, 1]
     projs = [torch.randn(n, width, generator=g).to(dtype).float() for n in lens]
-    refs = [_scan_reference(p.double(), off, H, dk, dv, decay) for p in projs]
+    refs = [_scan_reference(p.double(), off, H, dk, dv, decay, dtype) for p in projs]
     dec = torch.tensor(decay, device=dev())
     state = torch.full((4, H * dv * dk), float("nan"), device=dev())
     state[[3, 1, 0]] = 0.0                                       # slots as the storage leaves them when opened
@@ -336,6 +338,7 @@ def test_decay_scan_in_portions_side_by_side_and_in_slots_used_again(dtype, H, d
         live = [r for r in range(3) if at[r] < lens[r]]
         counts = [cuts[r].pop(0) for r in live]
         x = torch.cat([projs[r][at[r]:at[r] + c] for r, c in zip(live, counts)]).to(dtype).to(dev())
+        ops.silu_rows(x[:, off[0]:off[2] + H * dv])            # (the scan takes activated q, k, v)
         step = _step(counts, [at[r] for r in live], [slots[r] for r in live])
         o = torch.empty(x.shape[0], H * dv, device=dev())
         ops.decay_scan(x, off[0], off[1], off[2], dec, state, step, o, H, dk, dv)
@@ -343,16 +346,18 @@ def test_decay_scan_in_portions_side_by_side_and_in_slots_used_again(dtype, H, d
         for r, c in zip(live, counts):
             got[r].append(o[t:t + c].double().cpu())
             t, at[r] = t + c, at[r] + c
+    tol = 1e-4 if dtype == torch.float32 else 4e-3          # (bfloat16: an activation that rounds the other way)
     for r in range(3):
-        assert rel_err(torch.cat(got[r]).numpy(), refs[r].numpy()) <= 1e-4, r
+        assert rel_err(torch.cat(got[r]).numpy(), refs[r].numpy()) <= tol, r
     assert bool(torch.isnan(state[2]).all())                     # a slot nobody owns is not touched
     # a slot used again: zeroed, it gives the whole-prompt result in one go; a padding entry writes zeros
     state[1] = 0.0
     x = torch.cat([projs[0], projs[2]]).to(dtype).to(dev())
+    ops.silu_rows(x[:, off[0]:off[2] + H * dv])
     step = _step([lens[0], 1], [0, 0], [1, -1])
     o = torch.full((x.shape[0], H * dv), float("nan"), device=dev())
     ops.decay_scan(x, off[0], off[1], off[2], dec, state, step, o, H, dk, dv)
-    assert rel_err(o[:lens[0]].double().cpu().numpy(), refs[0].numpy()) <= 1e-4
+    assert rel_err(o[:lens[0]].double().cpu().numpy(), refs[0].numpy()) <= tol
     assert bool((o[lens[0]:] == 0).all())
     # not writable: the record stays as it is
     kept = state.clone()
@@ -375,8 +380,11 @@ def test_decay_scan_keeps_a_far_write_and_forgets_with_a_small_decay():
     decay = [0.9995, 0.5]
     state = torch.zeros(1, H * dv * dk, device=dev())
     o = torch.empty(T, H * dv, device=dev())
+    act = proj.to(dev())
+    ops.silu_rows(act)
+    assert float(act[0].abs().max()) == 0.0
     for lo, hi in ((0, 4), (4, 6), (6, 333), (333, T - 1), (T - 1, T)):     # cuts right before and after the write
-        ops.decay_scan(proj[lo:hi].to(dev()), 0, ko, vo, torch.tensor(decay, device=dev()), state,
+        ops.decay_scan(act[lo:hi], 0, ko, vo, torch.tensor(decay, device=dev()), state,
                        _step([hi - lo], [lo], [0]), o[lo:hi], H, dk, dv)
     silu = lambda z: z / (1 + np.exp(-z))
     v5 = silu(np.arange(1, dv + 1, dtype=np.float64))
@@ -432,6 +440,25 @@ def test_small_elementwise_kernels(dtype):
     want = 12.0 * torch.tanh(z.double().cpu() / 12.0)
     ops.softcap(z, 12.0)
     assert torch.allclose(z.double().cpu(), want, atol=1e-5) and float(z.abs().max()) <= 12.0
+
+
+@gpu
+@pytest.mark.parametrize("tokens", [3, 20, 40, 100, 300])
+def test_relu_gate_in_the_products_that_fuse_the_activation(tokens):
+    """Every size class of the gated product (weight streaming, tcgen05 for tens of tokens, the two-SM kernel for
+    hundreds) with the ReLU gate in its epilogue, against the plain formula; SiLU still is what it was."""
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(tokens)
+    hidden, inter = 256, 384
+    x = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16)
+    w = (0.1 * torch.randn(2 * inter, hidden, generator=g)).to(torch.bfloat16)
+    gu = x.double() @ w.double().T
+    for act, ref in (("relu", torch.relu(gu[:, :inter]) * gu[:, inter:]), ("silu", P.silu(gu[:, :inter]) * gu[:, inter:])):
+        got = ops.gated_linear(x.to(dev()), w.to(dev()), act)
+        assert rel_err(got.float().cpu().numpy(), ref.numpy()) <= 2e-2, act
+    # an exact zero wherever the gate is negative
+    got = ops.gated_linear(x.to(dev()), w.to(dev()), "relu").float().cpu()
+    assert bool((got[gu[:, :inter] < -0.05] == 0).all())
 
 
 @gpu
