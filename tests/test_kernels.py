@@ -1092,7 +1092,7 @@ def test_kernels_refuse_what_they_do_not_take():
     with pytest.raises(TypeError):
         ops.rmsnorm(torch.empty(2, 8, dtype=torch.float16, device=d), torch.zeros(2, 8, dtype=torch.float16, device=d),
                     torch.ones(8, device=d), 1e-6)
-    with pytest.raises(ValueError, match="head_dim"):
+    with pytest.raises(ValueError, match="larger than the generic"):
         c = _paged_case(torch.float32, 2, 1, 32, 8, [9], [1], None, seed=1)
         ops.paged_attention_generic(torch.empty(1, 2 * 320, device=d), c["q"], 640, c["kc"], c["vc"], c["bt"],
                                     c["token_req"], c["req_slot"], c["positions"], 1, 2, 1, 320, 8, None, 1.0, None)

@@ -78,7 +78,7 @@ def test_feed_forward_part(dtype):
     ref = P.gated_mlp(x, rt(t["gate_proj.weight"], dtype), rt(t["up_proj.weight"], dtype), rt(t["down_proj.weight"], dtype))
     assert rel_err(y.float().cpu().numpy(), ref.numpy()) <= tol(dtype)
     with pytest.raises(ValueError, match="activation"):
-        build("feed_forward", "gated_mlp", {"hidden_size": 8, "intermediate_size": 8, "activation": "relu"})
+        build("feed_forward", "gated_mlp", {"hidden_size": 8, "intermediate_size": 8, "activation": "gelu"})
 
 
 # ---------------------------------------------------------------------------
