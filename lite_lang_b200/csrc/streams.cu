@@ -30,7 +30,8 @@ __global__ void embed_streams_kernel(float* __restrict__ out, const T* __restric
   }
 }
 
-// One block per output row i (token r = rows ? rows[i] : i).  A thread takes VEC neighbouring columns.
+// Blocks (i, j): output row i (token r = rows ? rows[i] : i), the j-th 128 x VEC columns.  A thread takes VEC
+// neighbouring columns.
 // y: T [tokens, hidden] or null; y_parts: float32 [parts, tokens, hidden] partial sums of a split product, or null;
 // mix [S, S] (from, to), write [S], read [S] (null: all ones), alpha [1], w, b [hidden] (b null: none): float32.
 template <typename T, int VEC, int SM>      // SM: the most streams this instance takes (its register arrays)
@@ -54,7 +55,8 @@ stream_tanh_norm_kernel(T* __restrict__ out, float* __restrict__ X, const T* __r
   const int i = blockIdx.x;
   const int r = rows ? rows[i] : i;
   float* xr = X + (size_t)r * S * hidden;
-  for (int c = threadIdx.x * VEC; c < hidden; c += blockDim.x * VEC) {
+  // (elementwise over the columns: a row's columns are shared out over the blocks along y)
+  for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC; c < hidden; c += gridDim.y * blockDim.x * VEC) {
     float xs[SM][VEC];
 #pragma unroll
     for (int s = 0; s < SM; ++s) {
@@ -158,7 +160,7 @@ extern "C" int ll_stream_tanh_norm(int dtype, void* out, float* X, const void* y
   const bool wide = (hidden % 4) == 0 && ((uintptr_t)X % 16) == 0 && ((uintptr_t)out % 16) == 0 &&
                     ((uintptr_t)y % 16) == 0;
 #define ST_LAUNCH(VV, MM)                                                                                            \
-  ll_launch(stream_tanh_norm_kernel<T, VV, MM>, dim3(n_out), dim3(128), 0, stream, (T*)out, X, (const T*)y, y_parts, \
+  ll_launch(stream_tanh_norm_kernel<T, VV, MM>, dim3(n_out, (hidden / VV + 127) / 128), dim3(128), 0, stream, (T*)out, X, (const T*)y, y_parts, \
             parts, part_stride, mix, write, read, alpha, w, b, rows, write_back, S, hidden)
   LL_DISPATCH_DTYPE(dtype, {
     if (wide) {

@@ -5,6 +5,10 @@ own continuation property.  GPU: each mechanism's kernels alone (with inputs mad
 shows), whole prompts, token-by-token decoding through captured steps, portions down to two tokens, mixed
 batches with pages and slots used again, the command-line replay tool and greedy generation through the scheduler.
 """
+import json
+import os
+import subprocess
+import sys
 import types
 
 import numpy as np
@@ -553,9 +557,9 @@ def test_whole_decode_and_portions(name, dtype):
         s = mgr.open()
         assert close(_feed(runner, mgr, s, seqs[i]), refs[i], dtype), f"{name} whole {i}"
         mgr.close(s)
-    for i in (0, 2):                                        # a prompt, then 40 tokens one by one (captured steps)
+    for i, tail in ((0, 120), (2, 40)):                     # a prompt, then many tokens one by one (captured steps)
         s, n = mgr.open(), len(seqs[i])
-        head = n - 40
+        head = n - tail
         got = [_feed(runner, mgr, s, seqs[i][:head])] + [_feed(runner, mgr, s, seqs[i][t:t + 1]) for t in range(head, n)]
         assert close(np.concatenate(got), refs[i], dtype), f"{name} decode {i}"
         mgr.close(s)
@@ -664,3 +668,29 @@ def test_greedy_generation_through_the_scheduler():
             seq.append(o[k])
     st = engine.stats()
     assert st["graph_replays"] > 0
+
+
+@gpu
+def test_command_line_picks_the_model_by_its_configuration():
+    folder = write_folder("P", sharpen=3.0)
+    cfg, w = P.read_model_folder(folder)
+    prompt = [int(t) for t in np.random.default_rng(8).integers(0, cfg["vocab"], 11)]
+    ids = os.path.join(folder, "prompt.json")
+    with open(ids, "w") as fh:
+        json.dump([prompt], fh)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "lite_lang_b200.cli", "--model_path", folder, "--prompt_ids", ids, "--dtype", "fp32",
+           "--max_output_length", "6", "--page_size", "4", "--num_pages", "32", "--max_batch_size", "2",
+           "--temperature", "0", "--ignore_eos"]
+    res = subprocess.run(cmd, capture_output=True, text=True, cwd=root, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    out = json.loads(res.stdout.strip().splitlines()[-1])["outputs"][0]
+    seq = list(prompt)
+    for tok in out:
+        logits = P.forward(cfg, w, seq)[-1]
+        top2 = torch.topk(logits, 2).values
+        if float(top2[0] - top2[1]) < 1e-3:
+            break
+        assert tok == int(torch.argmax(logits))
+        seq.append(tok)
+    assert len(out) == 6
