@@ -234,7 +234,10 @@ extern "C" int ll_silu_rows(int dtype, void* x, long stride, int num_tokens, int
 }
 
 // y[t, :] = o[t, :] / sqrt(mean(o[t, :]^2) + eps) * weight * sigmoid(gate[t, :]); one block per token.
-template <typename T>
+// VEC = 4: four numbers an access, and rows of up to 256 x 4 x LO_PIECES numbers stay in registers between the sum
+// of squares and the output (longer rows are read again).
+#define LO_PIECES 4
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 linear_attn_out_kernel(T* __restrict__ y, const float* __restrict__ o, const float* __restrict__ weight,
                        const T* __restrict__ gate, long gate_stride, float eps, int width) {
@@ -243,14 +246,66 @@ linear_attn_out_kernel(T* __restrict__ y, const float* __restrict__ o, const flo
   LL_PDL_WAIT();
   const int t = blockIdx.x;
   const float* orow = o + (size_t)t * width;
+  const T* g = gate + (size_t)t * gate_stride;
+  const bool resident = width <= 256 * VEC * LO_PIECES;
+  float x[LO_PIECES][VEC];
   float ss = 0.f;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) ss = fmaf(orow[i], orow[i], ss);
+  auto load = [&](int c, float* v) {
+    if (VEC == 4) {
+      const float4 q = *reinterpret_cast<const float4*>(orow + c);
+      v[0] = q.x; v[1 % VEC] = q.y; v[2 % VEC] = q.z; v[3 % VEC] = q.w;
+    } else {
+      v[0] = orow[c];
+    }
+  };
+  auto store = [&](int c, const float* v, float inv) {
+    T gv[VEC], out[VEC];
+    float w[VEC];
+    if (VEC == 4) {
+      if (sizeof(T) == 2) *reinterpret_cast<uint2*>(gv) = *reinterpret_cast<const uint2*>(g + c);
+      else *reinterpret_cast<uint4*>(gv) = *reinterpret_cast<const uint4*>(g + c);
+      const float4 q = *reinterpret_cast<const float4*>(weight + c);
+      w[0] = q.x; w[1 % VEC] = q.y; w[2 % VEC] = q.z; w[3 % VEC] = q.w;
+    } else {
+      gv[0] = g[c];
+      w[0] = weight[c];
+    }
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) out[k] = from_f32<T>(v[k] * inv * w[k] / (1.0f + expf(-to_f32<T>(gv[k]))));
+    if (VEC == 4 && sizeof(T) == 2) *reinterpret_cast<uint2*>(y + (size_t)t * width + c) = *reinterpret_cast<const uint2*>(out);
+    else if (VEC == 4) *reinterpret_cast<uint4*>(y + (size_t)t * width + c) = *reinterpret_cast<const uint4*>(out);
+    else y[(size_t)t * width + c] = out[0];
+  };
+  if (resident) {
+#pragma unroll
+    for (int p = 0; p < LO_PIECES; ++p) {
+      const int c = (threadIdx.x + p * 256) * VEC;
+      if (c < width) {
+        load(c, x[p]);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) ss = fmaf(x[p][k], x[p][k], ss);
+      }
+    }
+  } else {
+    for (int c = threadIdx.x * VEC; c < width; c += 256 * VEC) {
+      load(c, x[0]);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) ss = fmaf(x[0][k], x[0][k], ss);
+    }
+  }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)width + eps);
-  const T* g = gate + (size_t)t * gate_stride;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    const float z = to_f32<T>(g[i]);
-    y[(size_t)t * width + i] = from_f32<T>(orow[i] * inv * weight[i] / (1.0f + expf(-z)));
+  if (resident) {
+#pragma unroll
+    for (int p = 0; p < LO_PIECES; ++p) {
+      const int c = (threadIdx.x + p * 256) * VEC;
+      if (c < width) store(c, x[p], inv);
+    }
+  } else {
+    for (int c = threadIdx.x * VEC; c < width; c += 256 * VEC) {
+      load(c, x[0]);
+      store(c, x[0], inv);
+    }
   }
 }
 
@@ -287,7 +342,15 @@ extern "C" int ll_decay_scan(int dtype, const void* proj, long stride, int q_off
 extern "C" int ll_linear_attn_out(int dtype, void* y, const float* o, const float* weight, const void* gate,
                                   long gate_stride, float eps, int num_tokens, int width, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
-  LL_DISPATCH_DTYPE(dtype, ll_launch(linear_attn_out_kernel<T>, dim3(num_tokens), dim3(256), 0, stream, (T*)y, o,
-                                     weight, (const T*)gate, gate_stride, eps, width));
+  const bool wide = (width % 4) == 0 && (gate_stride % 4) == 0 && ((uintptr_t)o % 16) == 0 &&
+                    ((uintptr_t)weight % 16) == 0 && ((uintptr_t)gate % 16) == 0 && ((uintptr_t)y % 16) == 0;
+  LL_DISPATCH_DTYPE(dtype, {
+    if (wide)
+      ll_launch(linear_attn_out_kernel<T, 4>, dim3(num_tokens), dim3(256), 0, stream, (T*)y, o, weight, (const T*)gate,
+                gate_stride, eps, width);
+    else
+      ll_launch(linear_attn_out_kernel<T, 1>, dim3(num_tokens), dim3(256), 0, stream, (T*)y, o, weight, (const T*)gate,
+                gate_stride, eps, width);
+  });
   return LL_LAUNCH_RESULT();
 }

@@ -16,6 +16,8 @@
 // Cache plane: K [num_pages, nkv, page_size, hd], V [num_pages, nkv, page_size, vd].
 #include "common.cuh"
 
+#define RS_MAX_PAIRS 128      // (the pairs kernel takes heads of up to 256 rotated channels)
+
 template <typename T> struct Pair;
 template <> struct Pair<float> { typedef float2 type; };
 template <> struct Pair<bf16> { typedef __nv_bfloat162 type; };
@@ -36,11 +38,18 @@ bias_rotate_store_pairs_kernel(T* __restrict__ qkv, long qkv_stride, const float
                                int nkv, int hd, int vd, const int* __restrict__ slot_map, T* __restrict__ k_cache,
                                T* __restrict__ v_cache, int page_size, long num_slots, int* status) {
   typedef typename Pair<T>::type P2;
+  __shared__ float cs[RS_MAX_PAIRS], sn[RS_MAX_PAIRS];      // the token's cos and sin, made once for all heads
   LL_PDL_TRIGGER();
   LL_PDL_WAIT();
   const int t = blockIdx.x;
   T* row = qkv + (size_t)t * qkv_stride;
   const float pos = (float)(positions ? positions[t] : 0);
+  for (int i = threadIdx.x; i < (rot_dim >> 1); i += blockDim.x) {
+    const float a = pos * freq[i];
+    cs[i] = cosf(a);
+    sn[i] = sinf(a);
+  }
+  __syncthreads();
   long slot = slot_map ? (long)slot_map[t] : -1;
   if (slot >= num_slots) {
     if (threadIdx.x == 0) set_status(status, LL_ERR_SLOT_RANGE);
@@ -61,8 +70,7 @@ bias_rotate_store_pairs_kernel(T* __restrict__ qkv, long qkv_stride, const float
         x.y += b2.y;
       }
       if (i < half) {
-        const float a = pos * freq[i];
-        const float c = cosf(a), s = sinf(a);
+        const float c = cs[i], s = sn[i];
         x = make_float2(x.x * c - x.y * s, x.y * c + x.x * s);
       }
       const P2 r = pair_from_f32<T>(x.x, x.y);
@@ -160,7 +168,7 @@ extern "C" int ll_bias_rotate_store(int dtype, void* qkv, long qkv_stride, const
   if (num_tokens <= 0) return 0;
   if (rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || hd <= 0 || vd <= 0) return (int)cudaErrorInvalidValue;
   const int esz = dtype == LL_DTYPE_F32 ? 4 : 2;
-  const bool pairs = (interleaved || rot_dim == 0) && (hd % 2) == 0 && (vd % 2) == 0 && (qkv_stride % 2) == 0 &&
+  const bool pairs = (interleaved || rot_dim == 0) && rot_dim <= 2 * RS_MAX_PAIRS && (hd % 2) == 0 && (vd % 2) == 0 && (qkv_stride % 2) == 0 &&
                      ((uintptr_t)qkv % (2 * esz)) == 0 && ((uintptr_t)bias % 8) == 0 &&
                      ((uintptr_t)k_cache % (2 * esz)) == 0 && ((uintptr_t)v_cache % (2 * esz)) == 0;
   LL_DISPATCH_DTYPE(dtype, {

@@ -411,16 +411,28 @@ def test_linear_attention_output_norm_gate_and_the_join_of_two_mixers(dtype):
     ops.linear_attn_out(y, o.to(dev()), w.to(dev()), gate.to(dev())[:, 3:3 + width], 1e-5)
     want = P.rms_norm(o.double(), w.double(), 1e-5) * P.sigmoid(gate.double()[:, 3:3 + width])
     assert rel_err(y.float().cpu().numpy(), want.numpy()) <= kernel_tol(dtype)
-    a = (torch.randn(T, width, generator=g) * 4).to(dtype)
-    b = (torch.randn(T, width, generator=g) * 0.01).to(dtype)       # two outputs of very different size
-    ba, wa, wb = torch.randn(width, generator=g), torch.randn(width, generator=g), torch.randn(width, generator=g)
-    out = torch.empty(T, width, dtype=dtype, device=dev())
-    ops.rms_pair_mean(out, a.to(dev()), ba.to(dev()), wa.to(dev()), b.to(dev()), wb.to(dev()), 3e-6)
-    want = 0.5 * (P.rms_norm(a.double() + ba.double(), wa.double(), 3e-6) + P.rms_norm(b.double(), wb.double(), 3e-6))
-    assert rel_err(out.float().cpu().numpy(), want.numpy()) <= kernel_tol(dtype)
-    ops.rms_pair_mean(out, a.to(dev()), None, wa.to(dev()), b.to(dev()), wb.to(dev()), 3e-6)
-    want = 0.5 * (P.rms_norm(a.double(), wa.double(), 3e-6) + P.rms_norm(b.double(), wb.double(), 3e-6))
-    assert rel_err(out.float().cpu().numpy(), want.numpy()) <= kernel_tol(dtype)
+    # the join: rows of every size class of its kernels (one to eight warps a row, a block a row), 11 rows so that
+    # the last block of the warp-a-row kernels is not full
+    for width, T in ((90, 7), (64, 11), (1536, 11), (3584, 11), (8200, 3), (40000, 2)):
+        a = (torch.randn(T, width, generator=g) * 4).to(dtype)
+        b = (torch.randn(T, width, generator=g) * 0.01).to(dtype)       # two outputs of very different size
+        ba, wa, wb = torch.randn(width, generator=g), torch.randn(width, generator=g), torch.randn(width, generator=g)
+        out = torch.empty(T, width, dtype=dtype, device=dev())
+        ops.rms_pair_mean(out, a.to(dev()), ba.to(dev()), wa.to(dev()), b.to(dev()), wb.to(dev()), 3e-6)
+        want = 0.5 * (P.rms_norm(a.double() + ba.double(), wa.double(), 3e-6) + P.rms_norm(b.double(), wb.double(), 3e-6))
+        assert rel_err(out.float().cpu().numpy(), want.numpy()) <= kernel_tol(dtype), width
+        ops.rms_pair_mean(out, a.to(dev()), None, wa.to(dev()), b.to(dev()), wb.to(dev()), 3e-6)
+        want = 0.5 * (P.rms_norm(a.double(), wa.double(), 3e-6) + P.rms_norm(b.double(), wb.double(), 3e-6))
+        assert rel_err(out.float().cpu().numpy(), want.numpy()) <= kernel_tol(dtype), width
+    # the output norm with aligned rows (four numbers an access), short and long
+    for width in (64, 1536, 5000):
+        o = torch.randn(T, width, generator=g) * 30
+        w = 1 + 0.1 * torch.randn(width, generator=g)
+        gate = torch.randn(T, width, generator=g).to(dtype)
+        y = torch.empty(T, width, dtype=dtype, device=dev())
+        ops.linear_attn_out(y, o.to(dev()), w.to(dev()), gate.to(dev()), 1e-5)
+        want = P.rms_norm(o.double(), w.double(), 1e-5) * P.sigmoid(gate.double())
+        assert rel_err(y.float().cpu().numpy(), want.numpy()) <= kernel_tol(dtype), width
 
 
 @gpu
