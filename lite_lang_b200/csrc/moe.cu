@@ -15,7 +15,7 @@
 
 // Wr: float32 [E, hidden]; x: T [tokens, hidden]; gates: float32 [tokens, E]; top_idx int32 / top_w float32
 // [tokens, top].  score_fn: 0 softmax over all experts, 1 sigmoid, 2 the `top` largest logits are chosen and
-// their weights are the softmax over the chosen logits only.  `bias` (float32 [E], optional) is added to the
+// their weights are a softmax taken over just those logits.  `bias` (float32 [E], optional) is added to the
 // logits.  With `shared_w` (float32 [tokens]) the router matrix has one more row, the gate of an expert that
 // every token uses: shared_w[t] = sigmoid(Wr[E] . x).  One block per token: its eight warps share out the experts
 // (the token's row waits in shared memory as float32), then the first warp scores and picks.

@@ -193,7 +193,7 @@ class StreamWrite(NamedTuple):
     """A sublayer's output that has not been written into a residual of several streams yet (``parts/streams.py``):
     X[t] <- sum_s mix[s, t] X[s] + write[t] * y.  The norm that reads the residual next applies it in its pass."""
     y: torch.Tensor           # [tokens, hidden] in the engine's dtype, or float32 partial sums [parts, tokens, hidden]
-    mix: torch.Tensor         # float32 [streams, streams], indexed [from, to]
+    mix: torch.Tensor         # float32 [streams, streams]: row = the stream read, column = the stream written
     write: torch.Tensor       # float32 [streams]
 
 

@@ -3,12 +3,12 @@
 q = silu(W_q x), k = silu(W_k x) (``heads`` x ``key_dim``) and v = silu(W_v x) (``heads`` x ``value_dim``);
 per head, token by token,
 
-    S_t = decay_h * S_(t-1) + k_t v_t^T,      o_t = S_t^T q_t        (no other scale)
+    S_t = decay_h * S_(t-1) + k_t v_t^T,      o_t = S_t^T q_t        (nothing else multiplies the scores)
 
 The heads' o side by side are RMS-normed as one vector with the weight ``norm``, multiplied by
-sigmoid(W_g x) and projected by W_o.  The state starts at zero, is float32 and lives in the request's record
-of the cache manager's state pool, so a request goes on in a later step, alone or beside others, from where
-it stopped.  Everything between the projections and the output projection is float32.
+sigmoid(W_g x) and projected by W_o.  A request's state is all zeros before its first token; it is float32 and
+lives in the request's record of the cache manager's state pool, so a request goes on in a later step, alone or
+beside others, from where it stopped.  Everything between the projections and the output projection is float32.
 Tensors: ``q``, ``k``, ``v``, ``g``, ``o``, ``norm``; ``decay`` is a parameter (one number a head).
 """
 

@@ -62,7 +62,7 @@ class RotaryComputed(PositionEncoding):
     f_i = theta^(-2i/rotary_dim) / ``position_scale`` (linear scaling of the positions; 1: none), computed in
     float64 on the host and rounded to float32 once.  No table, so no limit on the positions.  ``layout``:
     "interleaved" pairs channel 2i with 2i+1, "half_split" pairs i with i + rotary_dim/2; channels from
-    ``rotary_dim`` on pass unchanged.  (u, v) -> (u cos a - v sin a, v cos a + u sin a)."""
+    ``rotary_dim`` on are left as they are.  (u, v) -> (u cos a - v sin a, v cos a + u sin a)."""
 
     computed = True
     fuses_with_store = False

@@ -177,7 +177,7 @@ def test_streams_embedding_write_read_and_tanh_norm(dtype, S, hidden):
     assert rel_err(out.float().cpu().numpy(), ref(Xd, read.double().cpu()).numpy()) <= kernel_tol(dtype)
     ops.stream_tanh_norm(out, X, S, alpha, w, b, None)
     assert rel_err(out.float().cpu().numpy(), ref(Xd, torch.ones(S, dtype=P.F)).numpy()) <= kernel_tol(dtype)
-    # a pending write, all streams from the old ones (mix is indexed [from, to])
+    # a pending write: every new stream is made from the old ones (mix: row = stream read, column = stream written)
     newX = torch.einsum("ij,itw->jtw", mix.double().cpu(), Xd) + write.double().cpu()[:, None, None] * y.double().cpu()[None]
     X1 = X.clone()
     ops.stream_tanh_norm(out, X1, S, alpha, w, b, read, y, mix, write)
@@ -483,7 +483,7 @@ def test_relu_gate_in_the_products_that_fuse_the_activation(tokens):
                                                    (8, 3, 16, 8, 200)])
 def test_routed_gated_experts_part(dtype, E, top, ff, shared, tokens):
     """The part against the plain formulas, by the stacked way (few tokens, float32) and the grouped way (many
-    tokens, bfloat16): chosen experts, softmax over the chosen logits only, router bias, clamps on both sides of
+    tokens, bfloat16): chosen experts, weights by a softmax over just their logits, router bias, clamps on both sides of
     the limit, the shared expert with a limit of its own and its sigmoid gate."""
     from lite_lang_b200.config.spec import PartSpec
     from lite_lang_b200.parts import build_part
