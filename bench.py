@@ -457,7 +457,7 @@ def run_ours(args):
 
 
 # ---------------------------------------------------------------------------------------------------------
-# --compare nevurax: the Nevurax design beside Qwen2 at equal layer sizes (random weights)
+# --compare nevurax / redirax: that design beside Qwen2 at equal layer sizes (random weights)
 # ---------------------------------------------------------------------------------------------------------
 def _nevurax_shape(width, heads, kv_heads, head, inter, vocab, layers, window, experts, top):
     """A Nevurax model whose layers are as large as a Qwen2 layer of the given sizes: the mixers have as many
